@@ -24,6 +24,7 @@ class GroupLayout:
     stacked: bool                             # the default lay-out: K and V in one tensor
     window: int
     cache_ids: tuple[int, ...]
+    chunk: int = 0                            # chunked mask: pages stay until the request ends
 
     def bytes_per_page(self, page_size: int, itemsize: int) -> int:
         per_token = sum(h * w for h, w in self.planes)
@@ -47,8 +48,8 @@ def plan_groups(cache_specs: dict[int, object]) -> tuple[list[GroupLayout], dict
     for cid in sorted(cache_specs):
         s = cache_specs[cid]
         if isinstance(s, PagedKVSpec):
-            by_key.setdefault((s.layout(), s.planes is None, s.window), []).append(cid)
-    groups = [GroupLayout(k[0], k[1], k[2], tuple(v)) for k, v in by_key.items()]
+            by_key.setdefault((s.layout(), s.planes is None, s.window, s.chunk), []).append(cid)
+    groups = [GroupLayout(k[0], k[1], k[2], tuple(v), k[3]) for k, v in by_key.items()]
     where = {cid: g for g, gl in enumerate(groups) for cid in gl.cache_ids}
     return groups, where
 

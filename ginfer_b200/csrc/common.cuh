@@ -60,6 +60,16 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 inline int launch_status() { return (int)cudaGetLastError(); }
 
+// The first key the query at position p sees (the last one is p itself).  `span` is how the
+// attention kernels are told their mask: 0 = every earlier key; span > 0 = a sliding window of
+// `span` keys (p - c < span); span < 0 = chunks of -span positions counted from position 0 of the
+// sequence (a query sees the keys of its own chunk).  Never decreases with p.
+__host__ __device__ __forceinline__ int first_visible_key(int p, int span) {
+  if (span > 0) return p - span + 1 > 0 ? p - span + 1 : 0;
+  if (span < 0) return p / (-span) * (-span);
+  return 0;
+}
+
 // ---- programmatic dependent launch -------------------------------------------------------------
 // A kernel launched with the attribute may start while its predecessor in the stream still runs;
 // it must call pdl_wait() before it reads (or overwrites) anything the predecessor touches, and

@@ -1,0 +1,389 @@
+// Linear recurrences with decays over per-request state, for packed tokens of several requests:
+//
+//     S_t = diag(g_t) S_(t-1) + (c_t k_t) v_t^T        S: [D, Vd] a head, fp32, in the request's slot
+//     o_t = S_t^T q_t + skip_h v_t
+//
+// g_t is one decay per key channel (gated linear attention) or one per head (state-space duality:
+// k = B_t, q = C_t, c = the step size, skip = D_h).  q and k may be shared by groups of heads.
+//
+//   ssd_prepare_kernel        a thread a (token, channel): causal convolution over time (taps from
+//                             this step's rows, or from the slot where the portion starts later than
+//                             the tap reaches) + bias + SiLU on the x | B | C channels; step size
+//                             dt = softplus(dt + dt_bias) and decay exp(-exp(A_log_h) dt) per head.
+//   conv_state_kernel         a thread a (request, channel): the slot's last inputs after the step.
+//   gla_prepare_kernel        q * D^-1/2, k, v as fp32 and the decays sigmoid(z)^(1/tau) =
+//                             exp(log_sigmoid(z) / tau).
+//   decay_recurrence_kernel   a block a (request, head, tile of columns), token after token.  The
+//                             columns of S are independent: LP lanes share a column (DPER rows each,
+//                             in registers) and add their shares of o up by shuffles; the tokens'
+//                             operands come a chunk ahead through two stages of shared memory
+//                             (cp.async).  Lanes of a warp are laid out [LP][32 / LP columns], so
+//                             that a row of S is read and written in whole 32-byte sectors (LP = 4).
+//   gated_norm_kernel         a warp a (token, group of channels): RMS norm with a gate, the gate
+//                             before the norm (y = o silu(z), then y / rms(y) w) or behind it
+//                             (o / rms(o) w silu(z)); the weight per channel or shared by the groups.
+//
+// Everything here is fp32 arithmetic in both paths; only the projections that feed it and the
+// result of gated_norm_kernel have the activation dtype.
+#include "common.cuh"
+
+namespace gf {
+
+using bf = __nv_bfloat16;
+
+__device__ __forceinline__ float ds_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float ds_sigmoid(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float ds_log_sigmoid(float x) {
+  return fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
+}
+
+struct SsdDims {
+  int H, taps;
+  int channels;          // convolved columns (x | B | C) of a projection row
+  int conv_col;          // where they start in a projection row
+  int dt_col;            // where the H step sizes start
+  int state_stride;      // floats a slot
+  int conv_off;          // where the convolution inputs start in a slot
+};
+
+template <typename T>
+__global__ void ssd_prepare_kernel(const T* __restrict__ proj, int ld,
+                                   const float* __restrict__ conv_w,
+                                   const float* __restrict__ conv_b,
+                                   const float* __restrict__ dt_bias,
+                                   const float* __restrict__ A_log,
+                                   const float* __restrict__ state,
+                                   const int* __restrict__ seq_of_token,
+                                   const int* __restrict__ cu_seqlens,
+                                   const int* __restrict__ slot_ids, SsdDims dm,
+                                   float* __restrict__ xbc, float* __restrict__ rates) {
+  const int r = blockIdx.x;
+  const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+  pdl_trigger();
+  pdl_wait();
+  const int CH = dm.channels, H = dm.H, taps = dm.taps;
+  if (ch >= CH + H) return;
+  if (ch >= CH) {                                  // a head's step size and decay
+    const int h = ch - CH;
+    const float dt = ds_softplus(to_f32(proj[(size_t)r * ld + dm.dt_col + h]) + dt_bias[h]);
+    rates[(size_t)r * 2 * H + h] = expf(-expf(A_log[h]) * dt);
+    rates[(size_t)r * 2 * H + H + h] = dt;
+    return;
+  }
+  const int b = seq_of_token[r];
+  const int i = r - cu_seqlens[b];                 // place in this step's portion
+  const float* cs = state + (size_t)slot_ids[b] * dm.state_stride + dm.conv_off;
+  float acc = conv_b[ch];
+  for (int j = 0; j < taps; ++j) {
+    const int back = taps - 1 - j;
+    const int off = i - back;                      // place of the tap's input in the portion
+    const float x = off >= 0 ? to_f32(proj[(size_t)(r - back) * ld + dm.conv_col + ch])
+                             : cs[(size_t)(taps - 1 + off) * CH + ch];
+    acc = fmaf(conv_w[(size_t)ch * taps + j], x, acc);
+  }
+  xbc[(size_t)r * CH + ch] = acc * ds_sigmoid(acc);
+}
+
+template <typename T>
+__global__ void conv_state_kernel(const T* __restrict__ proj, int ld, float* __restrict__ state,
+                                  const int* __restrict__ cu_seqlens,
+                                  const int* __restrict__ slot_ids, SsdDims dm) {
+  const int b = blockIdx.y;
+  const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_trigger();
+  pdl_wait();
+  if (ch >= dm.channels) return;
+  const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
+  float* cs = state + (size_t)slot_ids[b] * dm.state_stride + dm.conv_off;
+  const int keep = dm.taps - 1;
+  // entry m holds the input (keep - m) tokens before the next one; ascending m reads only
+  // entries that are not yet overwritten
+  for (int m = 0; m < keep; ++m) {
+    const int idx = n - keep + m;                  // place in the portion, or before it
+    cs[(size_t)m * dm.channels + ch] =
+        idx >= 0 ? to_f32(proj[(size_t)(start + idx) * ld + dm.conv_col + ch])
+                 : cs[(size_t)(m + n) * dm.channels + ch];
+  }
+}
+
+// proj: q [H D] | k [H D] | v [H Vd] first in a row; z [T, H D] fp32.  out: [T, 3 H D + H Vd] fp32
+// laid out q | k | g | v.
+template <typename T>
+__global__ void gla_prepare_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ z,
+                                   int rows, int HD, int HV, float q_scale, float inv_tau,
+                                   float* __restrict__ out) {
+  const int width = 3 * HD + HV;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_trigger();
+  pdl_wait();
+  if (i >= (size_t)rows * width) return;
+  const int r = (int)(i / width), c = (int)(i - (size_t)r * width);
+  float y;
+  if (c < HD) y = to_f32(proj[(size_t)r * ld + c]) * q_scale;
+  else if (c < 2 * HD) y = to_f32(proj[(size_t)r * ld + c]);
+  else if (c < 3 * HD) y = expf(ds_log_sigmoid(z[(size_t)r * HD + c - 2 * HD]) * inv_tau);
+  else y = to_f32(proj[(size_t)r * ld + c - HD]);
+  out[i] = y;
+}
+
+// ------------------------------------------------------------------------------- the recurrence
+struct DecayDims {
+  int H, G, D, Vd;
+  int gD;                // D: a decay a key channel; 1: a decay a head
+  int ld_q, ld_k, ld_v, ld_g, ld_c;   // floats between the rows of two tokens
+  int state_stride;
+};
+
+__device__ __forceinline__ void ds_copy4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src)
+               : "memory");
+}
+__device__ __forceinline__ void ds_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void ds_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+constexpr int kDecayWarps = 4;
+constexpr int kDecayChunk = 8;
+
+template <int DPER, int LP>
+__global__ void __launch_bounds__(kDecayWarps * 32)
+decay_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ k,
+                        const float* __restrict__ v, const float* __restrict__ g,
+                        const float* __restrict__ c, const float* __restrict__ skip,
+                        float* __restrict__ state, const int* __restrict__ cu_seqlens,
+                        const int* __restrict__ slot_ids, DecayDims dm, float* __restrict__ o,
+                        int ld_o) {
+  constexpr int CW = 32 / LP;                      // columns a warp
+  constexpr int VT = kDecayWarps * CW;             // columns a block
+  constexpr int DP = DPER * LP;                    // key channels, padded
+  constexpr int ROW = 3 * DP + VT + 1;             // floats a token in a stage: q | k | g | v | c
+  extern __shared__ float stage[];                 // [2][kDecayChunk][ROW]
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int lp = lane / CW, vc = lane - lp * CW;
+  const int col0 = blockIdx.x * VT;
+  const int col = col0 + warp * CW + vc;
+  const int D = dm.D, Vd = dm.Vd, gk = h / (dm.H / dm.G);
+  const bool live = col < Vd;
+  // the padding rows of the stages: q = k = 0 for ever (cp.async never writes there)
+  for (int i = threadIdx.x; i < 2 * kDecayChunk * ROW; i += blockDim.x) stage[i] = 0.f;
+  pdl_trigger();
+  pdl_wait();
+  const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
+  float* S = state + (size_t)slot_ids[b] * dm.state_stride + (size_t)h * D * Vd;
+  float s[DPER];
+#pragma unroll
+  for (int i = 0; i < DPER; ++i) {
+    const int d = lp + LP * i;
+    s[i] = (live && d < D) ? S[(size_t)d * Vd + col] : 0.f;
+  }
+  const float sk = skip != nullptr ? skip[h] : 0.f;
+  __syncthreads();
+
+  auto fetch = [&](int chunk, int buf) {
+    const int t0 = chunk * kDecayChunk;
+    const int cnt = min(kDecayChunk, n - t0);
+    float* base = stage + (size_t)buf * kDecayChunk * ROW;
+    const int per = 2 * D + dm.gD + VT + 1;
+    for (int i = threadIdx.x; i < cnt * per; i += blockDim.x) {
+      const int t = i / per, e = i - t * per;
+      const size_t r = (size_t)(start + t0 + t);
+      float* row = base + t * ROW;
+      if (e < D) ds_copy4(row + e, q + r * dm.ld_q + (size_t)gk * D + e);
+      else if (e < 2 * D) ds_copy4(row + DP + e - D, k + r * dm.ld_k + (size_t)gk * D + e - D);
+      else if (e < 2 * D + dm.gD)
+        ds_copy4(row + 2 * DP + e - 2 * D, g + r * dm.ld_g + (size_t)h * dm.gD + e - 2 * D);
+      else if (e < per - 1) {
+        const int cc = e - 2 * D - dm.gD;
+        if (col0 + cc < Vd) ds_copy4(row + 3 * DP + cc, v + r * dm.ld_v + (size_t)h * Vd + col0 + cc);
+      } else if (c != nullptr) ds_copy4(row + 3 * DP + VT, c + r * dm.ld_c + h);
+    }
+    ds_commit();
+  };
+
+  const int chunks = (n + kDecayChunk - 1) / kDecayChunk;
+  if (chunks > 0) fetch(0, 0);
+  for (int ch = 0; ch < chunks; ++ch) {
+    ds_wait_all();
+    __syncthreads();                               // chunk ch has landed; the other stage is free
+    if (ch + 1 < chunks) fetch(ch + 1, (ch + 1) & 1);
+    const float* base = stage + (size_t)(ch & 1) * kDecayChunk * ROW;
+    const int cnt = min(kDecayChunk, n - ch * kDecayChunk);
+    for (int t = 0; t < cnt; ++t) {
+      const float* row = base + t * ROW;
+      const float vv = row[3 * DP + warp * CW + vc];
+      const float kv = (c != nullptr ? row[3 * DP + VT] : 1.f) * vv;
+      const float g1 = row[2 * DP];
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPER; ++i) {
+        const int d = lp + LP * i;
+        const float gd = dm.gD == 1 ? g1 : row[2 * DP + d];
+        s[i] = fmaf(gd, s[i], row[DP + d] * kv);
+        acc = fmaf(s[i], row[d], acc);
+      }
+#pragma unroll
+      for (int off = CW; off < 32; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+      if (lp == 0 && live)
+        o[(size_t)(start + ch * kDecayChunk + t) * ld_o + (size_t)h * Vd + col] = fmaf(sk, vv, acc);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < DPER; ++i) {
+    const int d = lp + LP * i;
+    if (live && d < D) S[(size_t)d * Vd + col] = s[i];
+  }
+}
+
+// ------------------------------------------------------------------------------- gated norm
+// o [rows, C] fp32; gate [rows, ...] (G = float or bf16) with row stride gate_ld; groups of gs
+// channels; w [C] or, shared, [gs].
+template <typename G, typename T>
+__global__ void gated_norm_kernel(const float* __restrict__ o, const G* __restrict__ gate,
+                                  int gate_ld, const float* __restrict__ w, int w_shared,
+                                  int gate_first, float eps, T* __restrict__ out, int units,
+                                  int groups, int gs) {
+  const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  pdl_trigger();
+  pdl_wait();
+  if (unit >= units) return;
+  const int r = unit / groups, gi = unit - r * groups;
+  const float* orow = o + (size_t)r * groups * gs + (size_t)gi * gs;
+  const G* grow = gate + (size_t)r * gate_ld + (size_t)gi * gs;
+  T* dst = out + (size_t)r * groups * gs + (size_t)gi * gs;
+  float ss = 0.f;
+  for (int j = lane; j < gs; j += 32) {
+    float y = orow[j];
+    if (gate_first) {
+      const float z = to_f32(grow[j]);
+      y *= z * ds_sigmoid(z);
+    }
+    ss = fmaf(y, y, ss);
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.f / sqrtf(ss / (float)gs + eps);
+  for (int j = lane; j < gs; j += 32) {
+    const float z = to_f32(grow[j]);
+    const float gz = z * ds_sigmoid(z);
+    const float wj = w[w_shared ? j : gi * gs + j];
+    const float y = gate_first ? orow[j] * gz * inv * wj : orow[j] * inv * wj * gz;
+    dst[j] = from_f32<T>(y);
+  }
+}
+
+}  // namespace gf
+
+using namespace gf;
+
+GF_DEFINE_PDL_SWITCH
+
+// proj: [T, ld]; the convolved channels start at conv_col, the H step sizes at dt_col.  xbc:
+// [T, channels] fp32; rates: [T, 2 H] fp32, decays first, then step sizes.  The slots' last inputs
+// are brought up to date by a second kernel.
+GF_EXPORT int gf_ssd_prepare(const void* proj, int ld, int conv_col, int dt_col,
+                             const float* conv_w, const float* conv_b, const float* dt_bias,
+                             const float* A_log, float* state, const int* seq_of_token,
+                             const int* cu_seqlens, const int* slot_ids, int T, int B, int H,
+                             int channels, int taps, int state_stride, int conv_off, float* xbc,
+                             float* rates, int dtype, void* stream) {
+  if (T <= 0) return 0;
+  if (taps < 1) return -3;
+  SsdDims dm;
+  dm.H = H, dm.taps = taps, dm.channels = channels, dm.conv_col = conv_col, dm.dt_col = dt_col;
+  dm.state_stride = state_stride, dm.conv_off = conv_off;
+  auto st = (cudaStream_t)stream;
+  const dim3 pgrid(T, (channels + H + 255) / 256), pblock(256);
+  int rc;
+  if (dtype == GF_F32)
+    rc = launch_kernel(ssd_prepare_kernel<float>, pgrid, pblock, 0, st, (const float*)proj, ld,
+                       conv_w, conv_b, dt_bias, A_log, (const float*)state, seq_of_token,
+                       cu_seqlens, slot_ids, dm, xbc, rates);
+  else
+    rc = launch_kernel(ssd_prepare_kernel<bf>, pgrid, pblock, 0, st, (const bf*)proj, ld, conv_w,
+                       conv_b, dt_bias, A_log, (const float*)state, seq_of_token, cu_seqlens,
+                       slot_ids, dm, xbc, rates);
+  if (rc || taps == 1) return rc;
+  const dim3 grid((channels + 127) / 128, B);
+  if (dtype == GF_F32)
+    return launch_kernel(conv_state_kernel<float>, grid, dim3(128), 0, st, (const float*)proj, ld,
+                         state, cu_seqlens, slot_ids, dm);
+  return launch_kernel(conv_state_kernel<bf>, grid, dim3(128), 0, st, (const bf*)proj, ld, state,
+                       cu_seqlens, slot_ids, dm);
+}
+
+GF_EXPORT int gf_gla_prepare(const void* proj, int ld, const float* z, int T, int HD, int HV,
+                             float q_scale, float inv_tau, float* out, int dtype, void* stream) {
+  if (T <= 0) return 0;
+  const size_t total = (size_t)T * (3 * HD + HV);
+  const dim3 grid((unsigned)((total + 255) / 256)), block(256);
+  auto st = (cudaStream_t)stream;
+  if (dtype == GF_F32)
+    return launch_kernel(gla_prepare_kernel<float>, grid, block, 0, st, (const float*)proj, ld, z,
+                         T, HD, HV, q_scale, inv_tau, out);
+  return launch_kernel(gla_prepare_kernel<bf>, grid, block, 0, st, (const bf*)proj, ld, z, T, HD,
+                       HV, q_scale, inv_tau, out);
+}
+
+// q, k: rows of G heads of D; v: rows of H heads of Vd; g: rows of H x gD decays (gD = D or 1);
+// c: rows of H factors on k, or null; skip: H weights of v in the output, or null; state: the
+// slots, S [H, D, Vd] first in each.  wide: sixteen lanes a column instead of four (few requests
+// with long portions).  Returns -3 for key sizes over 256.
+GF_EXPORT int gf_decay_recurrence(const float* q, int ld_q, const float* k, int ld_k,
+                                  const float* v, int ld_v, const float* g, int ld_g, int gD,
+                                  const float* c, int ld_c, const float* skip, float* state,
+                                  int state_stride, const int* cu_seqlens, const int* slot_ids,
+                                  int B, int H, int G, int D, int Vd, float* o, int ld_o, int wide,
+                                  void* stream) {
+  if (B <= 0) return 0;
+  if (G <= 0 || H % G || (gD != 1 && gD != D) || D <= 0 || D > 256) return -3;
+  DecayDims dm;
+  dm.H = H, dm.G = G, dm.D = D, dm.Vd = Vd, dm.gD = gD;
+  dm.ld_q = ld_q, dm.ld_k = ld_k, dm.ld_v = ld_v, dm.ld_g = ld_g, dm.ld_c = ld_c;
+  dm.state_stride = state_stride;
+  auto st = (cudaStream_t)stream;
+  const int lp = wide ? 16 : 4;
+  const int vt = kDecayWarps * (32 / lp);
+  const dim3 grid((Vd + vt - 1) / vt, H, B), block(kDecayWarps * 32);
+#define GF_GO(DPER, LP)                                                                            \
+  if (lp == LP && D <= LP * DPER) {                                                                \
+    const size_t smem = (size_t)2 * kDecayChunk * (3 * LP * DPER + kDecayWarps * (32 / LP) + 1) *  \
+                        sizeof(float);                                                             \
+    static OncePerDevice once;                                                                     \
+    const int rc = once.run([&] {                                                                  \
+      return cudaFuncSetAttribute(decay_recurrence_kernel<DPER, LP>,                               \
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+    });                                                                                            \
+    if (rc) return rc;                                                                             \
+    return launch_kernel(decay_recurrence_kernel<DPER, LP>, grid, block, smem, st, q, k, v, g, c,  \
+                         skip, state, cu_seqlens, slot_ids, dm, o, ld_o);                          \
+  }
+  GF_GO(4, 4)
+  GF_GO(8, 4)
+  GF_GO(16, 4)
+  GF_GO(32, 4)
+  GF_GO(64, 4)
+  GF_GO(1, 16)
+  GF_GO(2, 16)
+  GF_GO(4, 16)
+  GF_GO(8, 16)
+  GF_GO(16, 16)
+#undef GF_GO
+  return -3;
+}
+
+// o: [T, groups * gs] fp32 -> out in the activation dtype.  gate_dtype: the gate's own.
+GF_EXPORT int gf_gated_norm(const float* o, const void* gate, int gate_ld, int gate_dtype,
+                            const float* w, int w_shared, int gate_first, float eps, void* out,
+                            int T, int groups, int gs, int dtype, void* stream) {
+  const int units = T * groups;
+  if (units <= 0) return 0;
+  auto st = (cudaStream_t)stream;
+  const dim3 grid((units + 3) / 4), block(128);
+#define GF_GO(GT, OT)                                                                              \
+  return launch_kernel(gated_norm_kernel<GT, OT>, grid, block, 0, st, o, (const GT*)gate, gate_ld, \
+                       w, w_shared, gate_first, eps, (OT*)out, units, groups, gs)
+  if (gate_dtype == GF_F32 && dtype == GF_F32) GF_GO(float, float);
+  if (gate_dtype == GF_F32) GF_GO(float, bf);
+  if (dtype == GF_F32) GF_GO(bf, float);
+  GF_GO(bf, bf);
+#undef GF_GO
+}

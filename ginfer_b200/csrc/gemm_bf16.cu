@@ -113,7 +113,9 @@ __device__ __forceinline__ float silu_mul(float g, float u, const float* __restr
     const float limit = __ldg(act), alpha = __ldg(act + 1), shift = __ldg(act + 2);
     gg = fminf(gg, limit);
     uu = fminf(fmaxf(uu, -limit), limit);
-    return gg * (1.0f / (1.0f + expf(-alpha * gg))) * (uu + shift);
+    // alpha < 0: the gate's sigmoid sharpened to a step (relu)
+    const float sg = alpha < 0.f ? (gg > 0.f ? 1.0f : 0.0f) : 1.0f / (1.0f + expf(-alpha * gg));
+    return gg * sg * (uu + shift);
   }
   return gg * (1.0f / (1.0f + expf(-gg))) * uu;
 }

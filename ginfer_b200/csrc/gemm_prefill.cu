@@ -554,7 +554,9 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
                 const float limit = __ldg(bias), alpha = __ldg(bias + 1), shift = __ldg(bias + 2);
                 g = fminf(g, limit);
                 up = fminf(fmaxf(up, -limit), limit);
-                z[w] = g * (1.0f / (1.0f + expf(-alpha * g))) * (up + shift);
+                const float sg = alpha < 0.f ? (g > 0.f ? 1.0f : 0.0f)   // a step: relu
+                                             : 1.0f / (1.0f + expf(-alpha * g));
+                z[w] = g * sg * (up + shift);
               } else {
                 z[w] = g * (1.0f / (1.0f + expf(-g))) * up;
               }

@@ -151,6 +151,7 @@ __device__ __forceinline__ float clamped_glu(float g, float u, float limit, floa
                                              float up_shift) {
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
+  if (alpha < 0.f) return fmaxf(g, 0.f) * (u + up_shift);   // the sigmoid sharpened to a step: relu
   return g / (1.f + expf(-alpha * g)) * (u + up_shift);
 }
 

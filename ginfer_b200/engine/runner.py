@@ -271,7 +271,8 @@ class ModelRunner:
                 g = self.storage.group_of(cid)
                 return PagedKVBinding(self.storage.pages_of(cid), dev[f"block_table{g}"],
                                       dev[f"slot_mapping{g}"], self.page_size,
-                                      self.groups[g].window, entry.write_cache)
+                                      self.groups[g].window, entry.write_cache,
+                                      self.groups[g].chunk)
             if cid in self.storage.state:
                 return StateBinding(self.storage.state[cid], entry.write_cache)
             return None

@@ -148,6 +148,68 @@ def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float, up_shift: flo
     return out
 
 
+def postnorm(x: torch.Tensor, y: torch.Tensor, alpha: float, gamma: torch.Tensor, eps: float,
+             act_dtype: torch.dtype, want_act: bool = True, pairs=None):
+    """Norm after the sum: ``x' = s * gamma / rms(s)`` with ``s = alpha * x + y`` (fp32; ``x`` the
+    fp32 stream, ``y`` a sublayer's output in fp32 or the activation dtype, ``gamma`` fp32) and,
+    with ``want_act``, ``x'`` rounded to ``act_dtype``.  ``pairs = (pos_of_pair, weights or None,
+    top)``: ``y`` holds a row per (token, choice) pair of a routed feed-forward and the kernel
+    adds a token's rows up itself."""
+    _cuda(x, y, gamma)
+    assert x.dtype == torch.float32 and gamma.dtype == torch.float32
+    assert x.dim() == 2 and x.is_contiguous() and y.is_contiguous() and y.shape[1] == x.shape[1]
+    R, H = x.shape
+    pos = wgt = None
+    top = 0
+    if pairs is not None:
+        pos, wgt, top = pairs
+        assert pos.numel() == R * top and y.dtype == torch.float32
+    else:
+        assert y.shape == x.shape
+    out = torch.empty_like(x)
+    act = torch.empty((R, H), dtype=act_dtype, device=x.device) \
+        if want_act and act_dtype != torch.float32 else None
+    f = _fn("stream_ops", "gf_postnorm",
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_float,
+             c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    rc = f(_p(x), _p(y), _code(y.dtype), _p(pos), _p(wgt), int(top), float(alpha), _p(gamma),
+           float(eps), _p(out), _p(act), _code(act_dtype), R, H, _stream())
+    if rc == -4:
+        raise ValueError(f"rows of {H} channels do not fit the norm kernel's shared memory")
+    _ok(rc, "postnorm")
+    return out, (out if act_dtype == torch.float32 else act)
+
+
+def qk_wide_prepare(qkv: torch.Tensor, nh: int, nkv: int, hd: int, vd: int, k_off: int,
+                    v_off: int, q_w, k_w, eps: float, freqs, rot: int, positions: torch.Tensor,
+                    slot_mapping, kpages: torch.Tensor, vpages: torch.Tensor, v_first=None,
+                    mix=None) -> None:
+    """A token's q | k | v row before attention where q and k are normed over the whole
+    projection: ``q / rms(q) * q_w`` over all heads at once (``k`` likewise; no norm without
+    weights), rotation of the first ``rot`` channels of every head in pairs ``(i, i + rot/2)`` by
+    ``float(position) * freqs[i]``, values mixed with ``v_first`` (``(1 - mix) v + mix v_first``,
+    ``mix`` a one-element fp32 tensor on the device); q in place, k and v into the cache slot
+    ``slot_mapping`` names (``None``: nothing is written)."""
+    _cuda(qkv, q_w, k_w, freqs, positions, slot_mapping, kpages, vpages, v_first, mix)
+    assert qkv.dim() == 2 and qkv.stride(1) == 1
+    assert kpages.is_contiguous() and vpages.is_contiguous() and kpages.dtype == qkv.dtype
+    assert tuple(kpages.shape[-2:]) == (nkv, hd) and tuple(vpages.shape[-2:]) == (nkv, vd)
+    if v_first is not None:
+        assert v_first.dtype == qkv.dtype and v_first.stride(1) == 1 and mix.dtype == torch.float32
+        assert v_first.shape == (qkv.shape[0], nkv * vd)
+    f = _fn("qk_wide", "gf_qk_wide_prepare",
+            [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+             c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+             c_void_p, c_int, c_void_p])
+    rc = f(_p(qkv), qkv.stride(0), qkv.shape[0], nh, nkv, hd, vd, int(k_off), int(v_off), _p(q_w),
+           _p(k_w), float(eps), _p(freqs), int(rot), _p(positions), _p(slot_mapping), _p(kpages),
+           _p(vpages), _p(v_first), v_first.stride(0) if v_first is not None else 0, _p(mix),
+           _code(qkv.dtype), _stream())
+    if rc == -3:
+        raise ValueError(f"{rot} rotated channels must be an even number within the head of {hd}")
+    _ok(rc, "qk_wide_prepare")
+
+
 # ----------------------------------------------------------------------------- add + rmsnorm
 def add_rmsnorm(x: torch.Tensor, delta, gamma: torch.Tensor, eps: float, rows=None,
                 want_sum: bool = True, out_dtype=None):
@@ -217,16 +279,28 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
 
 
 # ----------------------------------------------------------------------------- attention
+def mask_span(window: int = 0, chunk: int = 0) -> int:
+    """How the attention kernels are told their mask, as one integer: 0 = every earlier key,
+    ``window`` > 0 = the last ``window`` keys, ``-chunk`` = the keys of the query's own chunk of
+    ``chunk`` positions (chunks are counted from position 0 of the sequence)."""
+    if window and chunk:
+        raise ValueError("a mask is a sliding window or chunks, not both")
+    return int(window) if window else -int(chunk)
+
+
 def paged_attention_simt(qkv, pages, block_table, seq_of_token, positions, nh, nkv, hd, scale,
-                         window, page_size):
-    _cuda(qkv, pages, block_table, seq_of_token, positions)
+                         window, page_size, vd=None):
+    """``window``: the mask as :func:`mask_span` gives it.  ``vd``: the values' head size where
+    it is not the keys' (``pages`` is then a pair of tensors)."""
+    _cuda(qkv, pages[0], pages[1], block_table, seq_of_token, positions)
     T = qkv.shape[0]
-    out = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
+    vd = hd if vd is None else int(vd)
+    out = torch.empty((T, nh * vd), dtype=qkv.dtype, device=qkv.device)
     f = _fn("attention_simt", "gf_paged_attention_simt",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
     rc = f(_p(qkv), qkv.stride(0), _p(pages[0]), _p(pages[1]), _p(block_table),
-           block_table.stride(0), _p(seq_of_token), _p(positions), _p(out), T, nh, nkv, hd,
+           block_table.stride(0), _p(seq_of_token), _p(positions), _p(out), T, nh, nkv, hd, vd,
            page_size, int(window), float(scale), _code(qkv.dtype), _stream())
     if rc == -3:
         raise ValueError(f"attention kernels take head sizes up to 256 and head counts that are "
@@ -243,14 +317,20 @@ def attention_fuses_rope(qkv: torch.Tensor, ctx, nh: int, nkv: int, hd: int) -> 
     return attention_bf16.fuses_rope(qkv, ctx, hd, nh, nkv)
 
 
-def paged_attention(qkv: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, ctx,
+def paged_attention(qkv: torch.Tensor, pages, block_table: torch.Tensor, ctx,
                     nh: int, nkv: int, hd: int, scale: float, window: int, page_size: int,
-                    rope=None) -> torch.Tensor:
+                    rope=None, vd: int | None = None) -> torch.Tensor:
     """Attention of the step's queries (first ``nh * hd`` columns of ``qkv``) over the paged
     cache; returns ``[T, nh * hd]``.  Picks the kernel by dtype, head size and batch shape.
     ``rope = (table or None, rotary_dim, write)`` where :func:`attention_fuses_rope`: q and k are
-    still unrotated and the new k and v not yet in the cache."""
+    still unrotated and the new k and v not yet in the cache.  ``window``: the mask as
+    :func:`mask_span` gives it.  ``vd``: the values' head size if it differs from ``hd``
+    (``pages`` is then the pair of the cache's two planes; the result is ``[T, nh * vd]``)."""
     from . import attention_bf16
+    if vd is not None and vd != hd:        # keys and values of different widths: the plain kernel
+        assert rope is None
+        return paged_attention_simt(qkv, pages, block_table, ctx.seq_of_token, ctx.positions, nh,
+                                    nkv, hd, scale, window, page_size, vd=vd)
     if qkv.dtype == torch.bfloat16:
         out = attention_bf16.try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window,
                                      page_size, rope=rope)

@@ -221,7 +221,7 @@ def fuses_rope(qkv, ctx, hd: int, nh: int, nkv: int) -> bool:
 def try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window, page_size, rope=None):
     """Run a bf16 kernel if one takes this head size; ``None`` hands the work to the plain
     fp32-arithmetic kernel.  ``rope``: see :func:`decode` (only where :func:`fuses_rope`)."""
-    if not supports(hd, nh, nkv):
+    if not supports(hd, nh, nkv) or window < 0:
         return None
     if ctx.decode_only:
         keys = ctx.max_kv_len if window <= 0 else min(window, ctx.max_kv_len)

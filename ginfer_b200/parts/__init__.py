@@ -7,5 +7,6 @@ from .base import (Block, Embedding, FeedForward, Head, LazyNorm, Mixer, Norm, P
                    StreamInput)
 from .plan import LayerSpec, ModelPlan, PartSpec, RunEntry, sequential_run
 from . import (attention, block, delta_rule, embedding, feed_forward, gated_attention,  # noqa: F401
-               latent_attention, norm, position, routed, stream_input)
+               latent_attention, linear_attention, norm, position, routed, state_space,
+               stream_input, wide_attention)
 from .model import DecoderModel

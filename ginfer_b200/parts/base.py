@@ -48,7 +48,7 @@ class TensorSpec:
 @dataclass(frozen=True)
 class PagedKVSpec:
     """What a mixer keeps of every position (``window == 0``) or of the last ``window``
-    positions, in pages.  By default keys and values of ``num_kv_heads`` heads of ``head_dim``
+    positions (or, with ``chunk``, of the chunk the sequence is in), in pages.  By default keys and values of ``num_kv_heads`` heads of ``head_dim``
     each.  ``planes`` names another lay-out: one ``(heads, width)`` per tensor kept of a token
     (one latent vector: ``((1, width),)``; keys and values of different widths:
     ``((heads, k_width), (heads, v_width))``)."""
@@ -56,6 +56,7 @@ class PagedKVSpec:
     head_dim: int
     window: int = 0
     planes: tuple[tuple[int, int], ...] | None = None
+    chunk: int = 0        # > 0: a query sees only the keys of its own chunk of this many positions
 
     def layout(self) -> tuple[tuple[int, int], ...]:
         return self.planes or ((self.num_kv_heads, self.head_dim),) * 2
@@ -78,6 +79,7 @@ class PagedKVBinding:
     page_size: int
     window: int
     write: bool
+    chunk: int = 0
 
 
 @dataclass

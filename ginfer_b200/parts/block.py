@@ -247,3 +247,63 @@ class ScaledPreNormBlock(Block):
 
 
 register_block("scaled_prenorm", ScaledPreNormBlock)
+
+
+class PostNormBlock(Block):
+    """Norms behind the sums: ``x <- norm1(alpha * x + mixer(x))``, then
+    ``x <- norm2(alpha * x + ff(x))``; the sublayers read the stream itself, and the normed sum IS
+    the stream.  ``x`` is fp32; the kernel that forms a normed sum also writes it rounded to the
+    activation dtype, which is what the next sublayer's products read (it travels to the next block
+    in ``ctx.extras["act_copy"]``, as with :class:`OutputNormBlock`).  A routed feed-forward may
+    hand over its pairs' rows (:class:`PairSum`) and the same kernel adds them up.  A layer
+    without a feed-forward is the first line alone."""
+
+    def __init__(self, layer_spec, alpha: float = 1.0):
+        self.spec = layer_spec
+        self.alpha = float(alpha)
+        self.mixer = make_part("mixer", layer_spec.mixer)
+        self.mixer_norm = make_part("norm", layer_spec.mixer_norm)
+        self.feed_forward = self.feed_forward_norm = None
+        if layer_spec.feed_forward is not None:
+            self.feed_forward = make_part("feed_forward", layer_spec.feed_forward)
+            self.feed_forward_norm = make_part("norm", layer_spec.feed_forward_norm)
+
+    def parts(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm,
+                                 self.feed_forward) if p is not None)
+
+    def tensor_specs(self):
+        out = []
+        for p in self.parts():
+            out.extend(p.tensor_specs())
+        return out
+
+    def load(self, tensors, dtype, device):
+        for p in self.parts():
+            p.load(tensors, dtype, device)
+
+    def forward(self, x, delta, ctx, cache):
+        from .base import PairSum
+        if delta is not None:
+            x = x.float() + delta.float()
+        elif x.dtype != torch.float32:
+            x = x.float()
+        kept = ctx.extras.get("act_copy")
+        h = kept[1] if kept is not None and kept[0] is x else x.to(ctx.dtype)
+        a = self.mixer.forward(h, ctx, cache)
+        x, h = self.mixer_norm.post(x, a, self.alpha, ctx.dtype)
+        if self.feed_forward is not None:
+            if self.feed_forward.can_defer_sum:
+                m = self.feed_forward.forward(h, ctx, defer_sum=True)
+            else:
+                m = self.feed_forward.forward(h, ctx)
+            if isinstance(m, PairSum):
+                x, h = self.feed_forward_norm.post(x, m.rows, self.alpha, ctx.dtype,
+                                                   pairs=(m.pos_of_pair, m.weights, m.top))
+            else:
+                x, h = self.feed_forward_norm.post(x, m, self.alpha, ctx.dtype)
+        ctx.extras["act_copy"] = (x, h)
+        return x, None
+
+
+register_block("postnorm", PostNormBlock)

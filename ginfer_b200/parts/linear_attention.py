@@ -1,0 +1,77 @@
+"""Gated linear attention: a linear recurrence with one decay per head and key channel.
+
+``q = W_q h * D^-1/2``, ``k = W_k h`` (``H`` heads of ``D``), ``v = W_v h`` (``H`` heads of
+``Vd``).  Decay ``alpha = sigmoid(z)^(1/tau)`` with ``z = W_a2 (W_a1 h) + b_a2`` laid out heads x
+``D``.  Per head ``S_t = diag(alpha_t) S_(t-1) + k_t v_t^T``, ``o_t = S_t^T q_t``.  Each head's
+``o`` is RMS-normed over its ``Vd`` channels with one weight vector shared by the heads; the heads
+side by side are multiplied by ``silu(W_g h)`` and projected by ``W_o``.
+
+State per request (one fp32 row of a slot): ``S [H, D, Vd]``.  The decay's second product leaves
+in 32-bit; its logarithm and exponential, the recurrence and the norm are fp32 arithmetic in both
+paths.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..ops import decay
+from .base import Mixer, StateSpec, TensorSpec, register_mixer
+
+
+class GatedLinearAttention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, key_dim: int, v_dim: int, tau: float,
+                 norm_eps: float = 1e-6, decay_rank: int = -1, prefix: str = "mix"):
+        self.hidden_size, self.H = int(hidden_size), int(num_heads)
+        self.D, self.Vd, self.tau = int(key_dim), int(v_dim), float(tau)
+        if not (self.tau > 0):
+            raise ValueError(f"tau must be > 0, got {tau}")
+        self.eps, self.decay_rank = float(norm_eps), int(decay_rank)     # -1: the file's
+        self.prefix = prefix + "." if prefix else ""
+
+    def _n(self, name):
+        return self.prefix + name
+
+    def tensor_specs(self):
+        W, HD, HV, r = self.hidden_size, self.H * self.D, self.H * self.Vd, self.decay_rank
+        return [TensorSpec(self._n("q"), (HD, W)), TensorSpec(self._n("k"), (HD, W)),
+                TensorSpec(self._n("v"), (HV, W)), TensorSpec(self._n("g"), (HV, W)),
+                TensorSpec(self._n("o"), (W, HV)),
+                TensorSpec(self._n("norm"), (self.Vd,), "norm32"),
+                TensorSpec(self._n("a1"), (r, W)), TensorSpec(self._n("a2"), (HD, r)),
+                TensorSpec(self._n("a2.b"), (HD,), "f32")]
+
+    def load(self, tensors, dtype, device):
+        t = {k: tensors[self._n(k)] for k in ("q", "k", "v", "g", "o", "norm", "a1", "a2", "a2.b")}
+        r = t["a1"].shape[0]
+        if t["a2"].shape[1] != r:
+            raise ValueError(f"{self.prefix}a1 and a2 disagree on their inner size")
+        rows = [t["q"], t["k"], t["v"], t["g"], t["a1"]]       # one product for all that reads h
+        n = sum(x.shape[0] for x in rows)
+        if -n % 8:
+            rows.append(torch.zeros((-n % 8, self.hidden_size), dtype=rows[0].dtype, device=device))
+        self.first = ops.Linear(torch.cat(rows, dim=0))
+        HD, HV = self.H * self.D, self.H * self.Vd
+        self.g_off = 2 * HD + HV
+        self.a1_off, self.r = self.g_off + HV, r
+        self.decay = ops.Linear(t["a2"], t["a2.b"].float(), out_dtype=torch.float32)
+        self.out = ops.Linear(t["o"], None, out_dtype=torch.float32)
+        self.norm_w = t["norm"].float().contiguous()
+
+    def cache_spec(self):
+        return StateSpec((self.H * self.D * self.Vd,), torch.float32)
+
+    def forward(self, x, ctx, cache):
+        H, D, Vd = self.H, self.D, self.Vd
+        HD, HV = H * D, H * Vd
+        p = self.first(x)                                   # [T, q | k | v | g | a1 (| pad)]
+        z = self.decay(p[:, self.a1_off:self.a1_off + self.r].contiguous())      # fp32 [T, H D]
+        f = decay.gla_prepare(p, z, HD, HV, D ** -0.5, self.tau)     # fp32 q | k | decays | v
+        o = decay.recurrence(f[:, :HD], f[:, HD:2 * HD], f[:, 3 * HD:], f[:, 2 * HD:3 * HD],
+                             cache.state, ctx, H, H, D, Vd)
+        y = decay.gated_norm(o, p[:, self.g_off:self.g_off + HV], self.norm_w, Vd, False, self.eps,
+                             ctx.dtype)
+        return self.out(y)
+
+
+register_mixer("gated_linear_attention", GatedLinearAttention)

@@ -25,6 +25,7 @@ class RMSNorm(Norm):
         self.weight_name = weight_name
         self.weight_offset = float(weight_offset)
         self.weight: torch.Tensor | None = None
+        self._w32: torch.Tensor | None = None      # the weight in 32-bit, made when first needed
 
     def tensor_specs(self):
         return [TensorSpec(self.weight_name, (self.size,),
@@ -32,6 +33,7 @@ class RMSNorm(Norm):
 
     def load(self, tensors, dtype, device):
         self.weight = tensors[self.weight_name]
+        self._w32 = None
         if self.weight_offset:
             self.weight = (self.weight.float() + self.weight_offset).contiguous()
 
@@ -40,6 +42,14 @@ class RMSNorm(Norm):
         stream ``x``; returns ``(x', x' in act_dtype or None)``."""
         w = self.weight if self.weight.dtype == torch.float32 else self.weight.float()
         return ops.outnorm_add(x, y, w, self.eps, act_dtype, want_act)
+
+    def post(self, x, y, alpha, act_dtype, want_act=True, pairs=None):
+        """For blocks whose norms sit behind the sums: ``x' = norm(alpha * x + y)`` on the fp32
+        stream ``x``; returns ``(x', x' in act_dtype or None)``.  ``pairs``: see
+        :func:`ginfer_b200.ops.postnorm`."""
+        if self._w32 is None:
+            self._w32 = self.weight.float().contiguous()
+        return ops.postnorm(x, y, alpha, self._w32, self.eps, act_dtype, want_act, pairs)
 
     def forward(self, x, delta=None, rows=None, want_sum=True, out_dtype=None):
         return ops.add_rmsnorm(x, delta, self.weight, self.eps, rows=rows, want_sum=want_sum,

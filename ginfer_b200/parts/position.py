@@ -58,11 +58,16 @@ class PairRotary(PositionEncoding):
     halves ``(i, i + dims/2)``.  ``scaling = {factor, low, high, original}`` stretches the long
     wavelengths: with ``l = 2 pi / f``, ``f`` stays where ``l < original/high``, becomes
     ``f / factor`` where ``l > original/low`` and ``(1 - s) f / factor + s f`` with
-    ``s = (original/l - low) / (high - low)`` in between.  Nothing is tabulated by position: the
+    ``s = (original/l - low) / (high - low)`` in between.  ``linear_factor`` divides every
+    frequency (positions stretched evenly).  Nothing is tabulated by position: the
     mixer's kernel forms ``float(p) * f_i`` in 32-bit and takes sine and cosine of it."""
 
-    def __init__(self, dims: int, base: float, scaling=None, interleaved: bool = True):
+    def __init__(self, dims: int, base: float, scaling=None, interleaved: bool = True,
+                 linear_factor: float = 1.0):
         self.dims, self.base = int(dims), float(base)
+        self.linear_factor = float(linear_factor)
+        if not (self.linear_factor > 0):
+            raise ValueError(f"linear_factor must be > 0, got {linear_factor}")
         if self.dims % 2 or self.dims < 0:
             raise ValueError(f"{self.dims} rotated channels: must be an even number")
         self.scaling = None if scaling is None else {k: float(scaling[k]) for k in
@@ -82,7 +87,7 @@ class PairRotary(PositionEncoding):
             mid = (1.0 - ramp) * f / sc["factor"] + ramp * f
             f = np.where(wave < sc["original"] / sc["high"], f,
                          np.where(wave > sc["original"] / sc["low"], f / sc["factor"], mid))
-        return f.astype(np.float32)
+        return (f / self.linear_factor).astype(np.float32)
 
     def load(self, tensors, dtype, device):
         self._freqs = torch.from_numpy(self.host_frequencies()).to(device)

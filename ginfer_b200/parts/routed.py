@@ -4,8 +4,9 @@ Router logits ``z = h W_r^T`` in 32-bit (float32 path: from the fp32 stream; bfl
 the bfloat16 rounding of ``h`` and the bfloat16 router matrix, whose products are exact in 32-bit
 and are added up in 32-bit by the tensor cores), scores ``softmax(z)`` over ALL experts, the ``top_k`` largest chosen; a token's output is the sum of the chosen experts' outputs
 weighted by their scores (as they are, or renormalised over the chosen ones with
-``renormalize``).  An expert is a clamped GLU (see :class:`ClampedGLU`) without biases, stored as
-``<prefix>.e<i>.gate|up|down``.
+``renormalize``: the softmax over the chosen logits alone).  An expert is a clamped GLU (see
+:class:`ClampedGLU`; an infinite limit, ``alpha`` 1 and no shift make it ``silu(g) * u``) without
+biases, stored as ``<prefix>.e<i>.gate|up|down``.
 
 Nothing returns to the host inside a step: the pairs (token, expert) are sorted by expert on the
 device and two grouped products walk over them.
@@ -52,7 +53,9 @@ class RoutedGLU(FeedForward):
         self.act = torch.tensor([self.limit, self.alpha, self.up_shift], dtype=torch.float32,
                                 device=device)
 
-    def forward(self, x, ctx):
+    can_defer_sum = True
+
+    def forward(self, x, ctx, defer_sum: bool = False):
         T = x.shape[0]
         idx, wgt = moe.route(self.router(x), self.top, self.renormalize)
         plan = moe.Plan(idx, self.E, moe.kernel_for(
@@ -60,7 +63,11 @@ class RoutedGLU(FeedForward):
             (self.intermediate_size, self.hidden_size)))
         y = moe.grouped_glu(x, self.w_gate_up, plan, self.limit, self.alpha, self.up_shift,
                             act=self.act)
-        return moe.combine(moe.grouped_down(y, self.w_down, plan), plan, wgt, T)
+        rows = moe.grouped_down(y, self.w_down, plan)
+        if defer_sum:
+            return PairSum(rows, plan.pos_of_pair, wgt, self.top,
+                           lambda: moe.combine(rows, plan, wgt, T))
+        return moe.combine(rows, plan, wgt, T)
 
 
 register_feed_forward("routed_glu", RoutedGLU)
