@@ -25,7 +25,7 @@ MAX_POSITIONS = 1 << 24
 RELU_GATE = -1.0
 
 
-def _mixer(cfg: PimidraConfig, kind: str, m) -> PartSpec:
+def _mixer(cfg: PimidraConfig, kind: str, m, value_mix=None) -> PartSpec:
     if kind == "mamba2":
         return PartSpec("state_space_dual", dict(
             hidden_size=cfg.width, num_heads=m["heads"], v_dim=m["vdim"], state_dim=m["state"],
@@ -46,7 +46,7 @@ def _mixer(cfg: PimidraConfig, kind: str, m) -> PartSpec:
         hidden_size=cfg.width, num_heads=m["heads"], num_kv_heads=m["kv_heads"],
         head_dim=m["dim"], v_dim=m["vdim"], scale=m["scale"], position=position,
         chunk=m["mask"]["size"] if m.get("mask") is not None else 0,
-        qk_norm_eps=cfg.norm_eps, value_mix=bool(m.get("v_mix")), prefix="mix"))
+        qk_norm_eps=cfg.norm_eps, value_mix=value_mix, prefix="mix"))
 
 
 def _feed_forward(cfg: PimidraConfig, mlp) -> PartSpec | None:
@@ -65,11 +65,15 @@ def _feed_forward(cfg: PimidraConfig, mlp) -> PartSpec | None:
 def pimidra_plan(cfg: PimidraConfig) -> ModelPlan:
     def norm(name):
         return PartSpec("rmsnorm", dict(size=cfg.width, eps=cfg.norm_eps, weight_name=name))
-    layers = []
+    layers, mixing = [], False
     for i, L in enumerate(cfg.layers):
         ff = _feed_forward(cfg, L.mlp)
+        role = None
+        if L.type == "attention" and L.mixer.get("v_mix"):
+            # the first layer that mixes its values is the one whose values the others mix in
+            role, mixing = ("mix" if mixing else "source"), True
         layers.append(LayerSpec(
-            prefix=f"l{i}", mixer=_mixer(cfg, L.type, L.mixer), feed_forward=ff,
+            prefix=f"l{i}", mixer=_mixer(cfg, L.type, L.mixer, role), feed_forward=ff,
             mixer_norm=norm("norm1"), feed_forward_norm=norm("norm2") if ff else None,
             block=PartSpec("postnorm", dict(alpha=cfg.postln_alpha))))
     return ModelPlan(

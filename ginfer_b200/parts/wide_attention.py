@@ -8,10 +8,11 @@ dims/2)``).  ``score = q.k * scale`` over the keys the mask lets the query see (
 it, a sliding window, or the query's own chunk of ``chunk`` positions counted from position 0 of
 the sequence), softmax; query head ``n`` reads kv head ``n // (H / G)``.
 
-**Value mixing** (``value_mix``): the first layer of a model that mixes leaves its values of the
-step's tokens in ``ctx.extras`` (under ``value_mix_key``); every later mixing layer replaces its
-own by ``(1 - lambda) v + lambda v_first`` with its scalar tensor ``vmix``, and caches the mixed
-values.  (The first layer owns a ``vmix`` too and does not use it.)
+**Value mixing** (``value_mix``): the layer that is the ``"source"`` (the first layer of a model
+that mixes) leaves its values of the step's tokens in ``ctx.extras`` (under ``value_mix_key``);
+every layer with ``"mix"`` replaces its own by ``(1 - lambda) v + lambda v_first`` with its scalar
+tensor ``vmix``, and caches the mixed values.  (The source owns a ``vmix`` too and does not use
+it.)  Which layer is which is the plan's to say: a step's context may be run more than once.
 
 One product over the joined matrices gives q, k and v; one kernel norms, rotates, mixes and writes
 the cache; the attention kernels of the plain grouped-query mixer run over that cache where keys
@@ -30,7 +31,7 @@ class WideNormAttention(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  v_dim: int, scale: float, position: PartSpec, window: int = 0, chunk: int = 0,
                  qk_norm: bool = True, qk_norm_eps: float = 1e-6, bias: bool = True,
-                 value_mix: bool = False, value_mix_key: str = "value_mix",
+                 value_mix: str | None = None, value_mix_key: str = "value_mix",
                  prefix: str = "mix"):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads are not a multiple of {num_kv_heads} kv heads")
@@ -41,7 +42,9 @@ class WideNormAttention(Mixer):
         self.hd, self.vd = int(head_dim), int(v_dim)
         self.scale, self.window, self.chunk = float(scale), int(window), int(chunk)
         self.qk_norm, self.eps, self.bias = bool(qk_norm), float(qk_norm_eps), bool(bias)
-        self.value_mix, self.mix_key = bool(value_mix), value_mix_key
+        if value_mix not in (None, "source", "mix"):
+            raise ValueError(f"value_mix is None, 'source' or 'mix', not {value_mix!r}")
+        self.value_mix, self.mix_key = value_mix, value_mix_key
         self.prefix = prefix + "." if prefix else ""
         self.position = make_part("position", position)
         if not hasattr(self.position, "frequencies") or self.position.interleaved:
@@ -101,11 +104,11 @@ class WideNormAttention(Mixer):
         nh, nkv, hd, vd = self.nh, self.nkv, self.hd, self.vd
         qkv = self.qkv(x)
         v_first = None
-        if self.value_mix:
-            v_first = ctx.extras.get(self.mix_key)
-            if v_first is None:       # the first mixing layer: its values are what the others mix in
-                ctx.extras[self.mix_key] = qkv[:, self.v_off:self.v_off + nkv * vd]
-            elif v_first.shape[1] != nkv * vd:
+        if self.value_mix == "source":        # its values are what the later layers mix in
+            ctx.extras[self.mix_key] = qkv[:, self.v_off:self.v_off + nkv * vd]
+        elif self.value_mix == "mix":
+            v_first = ctx.extras[self.mix_key]
+            if v_first.shape != (qkv.shape[0], nkv * vd):
                 raise ValueError("layers that mix their values must agree on the values' size")
         ops.qk_wide_prepare(qkv, nh, nkv, hd, vd, self.k_off, self.v_off, self.q_w, self.k_w,
                             self.eps, self.position.frequencies(), self.position.dims,
