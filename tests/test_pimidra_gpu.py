@@ -117,7 +117,7 @@ def test_the_oracle_without_a_mechanism_is_far_from_the_oracle(tmp_path_factory,
     full = expected(d, cfg, reqs)["r0"]
     less = expected(d, cfg, reqs, without=(without,))["r0"]
     rows = {("r0", p): less[p].astype(np.float32) for p in range(40, 90)}
-    assert row_errors(rows, {"r0": full})[2] > 0.05
+    assert row_errors(rows, {"r0": full})[2] > 0.01        # the float32 limit is 3e-4
 
 
 # ----------------------------------------------------------------------------- cuts of the same work
