@@ -19,7 +19,8 @@
 // cp.async and read by ldmatrix.  Scores, the running maximum, the sum and the output accumulator
 // are fp32 (the reference keeps S, P, the maximum and O in bf16:
 // flash_gqa_varlen_kernel.cu:169-172,220-257); P is rounded to bf16 for the P*V product.
-// Visibility: the query at position p sees key c iff c <= p and (window == 0 or p - c < window).
+// Visibility: the query at position p sees the keys first_visible_key(p, window) .. p (common.cuh:
+// `window` > 0 is a sliding window, < 0 chunks of -window positions, 0 every earlier key).
 #include <mutex>
 
 #include "attention_mma.cuh"
@@ -143,7 +144,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
   if (!late_wait) pdl_wait();
   const int row = cu_seqlens_q ? cu_seqlens_q[b] : b;         // null: request b is row b
   const int p = positions[row];
-  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int lo = first_visible_key(p, window);
   const int nkeys = p - lo + 1;
   int per = (nkeys + splits - 1) / splits;
   per = (per + KT - 1) / KT * KT;
@@ -502,7 +503,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap,
   if (!late_wait) pdl_wait();
   const int row = cu_seqlens_q ? cu_seqlens_q[b] : b;
   const int p = positions[row];
-  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int lo = first_visible_key(p, window);
   const int lo_al = lo / KT * KT;                               // tiles start on tile boundaries
   const int nkeys = p - lo_al + 1;
   const int pieces = splits * parts;
@@ -885,7 +886,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
   }
   // keys this tile can see: from the window's start of its first row to its last row's position
   const int p_first = pos0 + r0, p_last = pos0 + r0 + rows - 1;
-  const int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;
+  const int key_lo = first_visible_key(p_first, window);
   const int begin = key_lo / KT * KT, end = p_last + 1;
   const int ntiles = (end - begin + KT - 1) / KT;
   int lp_base = 0;
@@ -916,11 +917,11 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
       const int r = warp * WROWS + mt * 16 + g + 8 * i;
       const int p = pos0 + r0 + r;
       hi2[mt][i] = r < rows ? p : -1;          // rows past the end see nothing
-      lo2[mt][i] = window > 0 ? max(0, p - window + 1) : 0;
+      lo2[mt][i] = first_visible_key(p, window);
     }
   }
   const int warp_hi = min(p_last, pos0 + r0 + warp * WROWS + WROWS - 1);
-  const int warp_lo = window > 0 ? max(0, pos0 + r0 + warp * WROWS - window + 1) : 0;
+  const int warp_lo = first_visible_key(pos0 + r0 + warp * WROWS, window);
   const int mi = lane >> 3, lr = lane & 7;
   const bf16* qw = qs + (warp * WROWS + (mi & 1) * 8 + lr) * ROW + (mi >> 1) * 8;
 
@@ -963,7 +964,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
     // interior tile: every row of the warp sees all of its keys
     const int first_p = pos0 + r0 + warp * WROWS;
     const bool interior = col0 + KT - 1 <= first_p && warp * WROWS + WROWS <= rows &&
-                          (window <= 0 || col0 >= first_p + WROWS - 1 - window + 1);
+                          col0 >= first_visible_key(first_p + WROWS - 1, window);
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
       if (interior)

@@ -1,4 +1,4 @@
-// Prefill attention on the 5th-generation tensor cores: varlen, causal (+ sliding window), GQA,
+// Prefill attention on the 5th-generation tensor cores: varlen, causal (+ sliding window or chunks), GQA,
 // over the paged cache.  Compiled for one head size (-DGF_HEAD_DIM = 64 or 128).
 //
 // One CTA owns 128 query rows of one head of one request.  Keys are visited in tiles of 128, and
@@ -420,7 +420,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     it.rows = min(QT, q_len - it.r0);
     const int p_first = it.pos0 + it.r0;
     it.p_last = it.pos0 + it.r0 + it.rows - 1;
-    it.key_lo = window > 0 ? max(0, p_first - window + 1) : 0;
+    it.key_lo = first_visible_key(p_first, window);
     it.j0 = it.key_lo / KT;
     it.ntiles = it.p_last / KT - it.j0 + 1;
     return 1;
@@ -695,7 +695,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       const int mine = tiles_of(ntiles, s);
       const int p = pos00 + r;                                 // this row's position
       const bool live = r < rows;
-      const int lo = window > 0 ? max(0, p - window + 1) : 0;
+      const int lo = first_visible_key(p, window);
       const int wp0 = pos00 + qd * 32;                         // position of the warp's first row
       const bool tr = r == 0;
       float m_used = -INFINITY;        // the maximum the accumulated P and l are scaled by
@@ -711,7 +711,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const int col0 = (j0 + i) * KT;                        // first key of the tile
         // every row of this warp sees all of the tile's keys: no comparisons
         const bool interior = col0 + KT - 1 <= wp0 && qd * 32 + 32 <= rows &&
-                              (window <= 0 || col0 >= wp0 + 31 - window + 1);
+                              col0 >= first_visible_key(wp0 + 31, window);
         // ---- the whole row of S into registers
         float v[KT];
 #pragma unroll

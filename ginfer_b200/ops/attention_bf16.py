@@ -220,11 +220,12 @@ def fuses_rope(qkv, ctx, hd: int, nh: int, nkv: int) -> bool:
 
 def try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window, page_size, rope=None):
     """Run a bf16 kernel if one takes this head size; ``None`` hands the work to the plain
-    fp32-arithmetic kernel.  ``rope``: see :func:`decode` (only where :func:`fuses_rope`)."""
-    if not supports(hd, nh, nkv) or window < 0:
+    fp32-arithmetic kernel.  ``rope``: see :func:`decode` (only where :func:`fuses_rope`).
+    ``window``: the mask as ``ops.mask_span`` gives it (negative: chunks)."""
+    if not supports(hd, nh, nkv):
         return None
     if ctx.decode_only:
-        keys = ctx.max_kv_len if window <= 0 else min(window, ctx.max_kv_len)
+        keys = min(abs(window), ctx.max_kv_len) if window else ctx.max_kv_len
         splits, parts = decode_partition(ctx.num_seqs, nh, nkv, keys)
         if ctx.extras.get("decode_splits"):
             splits, parts = ctx.extras["decode_splits"], 1
@@ -242,7 +243,7 @@ def try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window, page_size,
         nd += 1
     out, cu, kv_lens, table, max_q = None, ctx.cu_seqlens_q, ctx.kv_lens, block_table, ctx.max_q_len
     if 0 < nd < B and len(q_lens) == B:
-        keys = ctx.max_kv_len if window <= 0 else min(window, ctx.max_kv_len)
+        keys = min(abs(window), ctx.max_kv_len) if window else ctx.max_kv_len
         out = torch.empty((qkv.shape[0], nh * hd), dtype=torch.bfloat16, device=qkv.device)
         splits, parts = decode_partition(nd, nh, nkv, keys)
         decode(qkv, pages, block_table[:nd], None, ctx.positions, nd, nh, nkv, hd, scale, window,

@@ -149,7 +149,9 @@ def _paged_case(B_lens, q_lens, nh, nkv, hd, P, window, dtype, seed=0, spike=Tru
         q = torch.randn(q_lens[b], nh, hd, generator=g)
         if spike and n > 40:
             # one far key stands out for one query: scale them so that its score dominates
-            far = 3 if window <= 0 else max(0, n - min(window, n))   # the oldest visible key
+            far = 3 if window == 0 else max(0, n - min(window, n))   # the oldest visible key
+            if window < 0:                                           # chunks of -window positions
+                far = (n - 1) // -window * -window
             q[-1, 0] = 0
             q[-1, 0, 0] = 30.0
             k[far, 0] = 0
@@ -177,6 +179,8 @@ def _paged_case(B_lens, q_lens, nh, nkv, hd, P, window, dtype, seed=0, spike=Tru
         for r in range(ql):
             p = n - ql + r
             lo = max(0, p - window + 1) if window > 0 else 0
+            if window < 0:
+                lo = p // -window * -window
             for h in range(nh):
                 kvh = h // (nh // nkv)
                 s = (kk[lo:p + 1, kvh] @ q[r, h]) * scale
@@ -222,6 +226,10 @@ ATT_CASES = [
     ([130, 40, 260], [130, 1, 37], 4, 2, 80, 16, 0),
     ([200, 33], [64, 33], 2, 1, 112, 8, 20),
     ([300, 70], [5, 70], 6, 2, 192, 16, 50),
+    # a negative window: chunks of that many positions counted from position 0
+    ([300, 129, 77], [100, 1, 77], 4, 2, 64, 16, -37),
+    ([700, 90], [65, 90], 6, 3, 64, 16, -96),
+    ([200, 33], [64, 33], 2, 1, 48, 8, -1),
 ]
 
 
@@ -261,6 +269,11 @@ TC_CASES = [
     # second CTA's keys are all behind the window's start for the first rows)
     ([1800, 900], [700, 900], 6, 2, 128, 16, 700),
     ([3000], [130], 4, 1, 64, 8, 0),
+    # chunks (a negative window): shorter and longer than a key tile, and of one position
+    ([700, 90], [65, 90], 6, 3, 64, 16, -96),
+    ([1800, 900], [700, 900], 6, 2, 128, 16, -700),
+    ([640, 400], [128, 400], 2, 1, 128, 16, -50),
+    ([300], [300], 2, 2, 64, 16, -1),
 ]
 
 
@@ -304,6 +317,8 @@ DEC_CASES = [
     ([2049, 17], 40, 2, 64, 16, 0),               # 20 query heads per kv head: two chunks of 16
     ([130, 40, 700], 6, 2, 80, 16, 0),            # five steps of 16 channels
     ([300, 70], 6, 2, 192, 8, 50),
+    ([700, 90, 97], 6, 3, 64, 16, -96),           # chunks; the last request sees its own key only
+    ([300, 129, 77], 5, 5, 48, 4, -33),
 ]
 
 
@@ -330,6 +345,8 @@ DEC_TMA_CASES = [   # what the kernel that loads by TMA serves: page sizes and h
     ([4100], 18, 2, 64, 16, 0),                   # 9 query heads per kv head: two chunks of 8
     ([300, 70, 8], 4, 2, 256, 8, 0),              # 64 boxes a tile: two for each lane of the loader
     ([600, 70, 9], 6, 2, 192, 16, 40),            # three 64-channel parts a row
+    ([1500, 700, 1441], 6, 3, 128, 16, -130),     # chunks that start inside a tile
+    ([961, 960], 4, 2, 64, 16, -96),              # the first and the last position of a chunk
 ]
 
 
