@@ -260,7 +260,7 @@ def prefill_timed(eng, tokens: int, reps: int, warmup: int, seed: int):
 
 
 # ----------------------------------------------------------------------------- another design
-# ``--design vilepel|zolapel``: prefill and decode throughput of another design at layer sizes that
+# ``--design vilepel|zolapel|pimidra``: prefill and decode throughput of another design at layer sizes that
 # resemble a real model's (random weights), beside Qwen2 at equal width, heads, feed-forward size
 # and layer count.  The default workload and its JSON line are untouched by this option.
 def vilepel_config(width, heads, dim, rot, vdim, rank, window, ff, experts, top, expert_ff,
@@ -299,6 +299,39 @@ def zolapel_config(width, heads, kv_heads, dim, window, experts, top, expert_ff,
             "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp} for _ in range(layers)]}
 
 
+def pimidra_config(width, heads, kv_heads, dim, chunk, ff, experts, top, expert_ff, ssd_heads,
+                   ssd_vdim, state, layers, vocab=32768):
+    """Layers in turns of four: chunked attention with mixed values / dense, state-space / routed,
+    attention / routed, gated linear attention / dense."""
+    def attention():
+        return {"type": "attention", "mixer": {
+            "heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+            "mask": {"size": chunk}, "v_mix": True,
+            "rot": {"base": 10000.0, "dims": dim // 2, "scaling": {"factor": 8.0}}}}
+
+    def ssd():
+        return {"type": "mamba2", "mixer": {"heads": ssd_heads, "vdim": ssd_vdim, "state": state,
+                                            "groups": 1, "conv": 4, "norm_groups": 1}}
+
+    def gla():
+        return {"type": "gla", "mixer": {"heads": heads, "dim": dim, "vdim": dim, "tau": 16.0,
+                                         "decay_rank": 16}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
+    kinds = [(attention, dense), (ssd, moe), (attention, moe), (gla, dense)]
+    return {"architecture": "Pimidra", "width": width, "vocab": vocab, "norm": {"eps": 1e-5},
+            "postln_alpha": 2.0, "torch_dtype": "bfloat16",
+            "layers": [dict(kinds[i % 4][0](), mlp=kinds[i % 4][1]) for i in range(layers)]}
+
+
+PIMIDRA_SIZES = {
+    # width, heads, kv heads, dim, chunk, dense ff, experts, top, expert ff, state-space heads,
+    # their value size, state size
+    "s": (1024, 8, 2, 64, 512, 2816, 16, 2, 704, 32, 64, 64),
+    "m": (2048, 16, 4, 128, 1024, 5632, 32, 4, 1408, 64, 64, 128),
+}
+
+
 ZOLAPEL_SIZES = {
     # width, heads, kv heads, dim, window, experts, top, expert ff, side dim
     "s": (1024, 8, 2, 64, 512, 16, 2, 1056, 64),
@@ -330,6 +363,17 @@ def design_configs(design: str, name: str, layers: int) -> dict:
                           intermediate_size=2 * top * eff // 3, vocab_size=32768,
                           use_sliding_window=True, sliding_window=window, max_window_layers=0),
         }
+    if design == "pimidra":
+        # beside it the closest design the engine has, Vilepel (attention with a bounded reach and a
+        # recurrent mixer in turns, dense and routed feed-forwards, an fp32 stream), at the same
+        # width, heads, head size, feed-forward and expert sizes, reach and layer count
+        width, heads, kv, dim, chunk, ff, experts, top, eff, sh, sv, state = PIMIDRA_SIZES[name]
+        return {
+            "pimidra": pimidra_config(width, heads, kv, dim, chunk, ff, experts, top, eff, sh, sv,
+                                      state, layers),
+            "vilepel": vilepel_config(width, heads, dim, dim // 2, dim, width // 4, chunk, ff,
+                                      experts, top, eff, layers),
+        }
     width, heads, dim, rot, vdim, rank, window, ff, experts, top, eff = DESIGN_SIZES[name]
     return {
         "vilepel": vilepel_config(width, heads, dim, rot, vdim, rank, window, ff, experts, top,
@@ -346,10 +390,12 @@ def run_design(args) -> int:
 
     from ginfer_b200.engine.llm import Engine
     out = {"design": args.design,
-           "beside": "qwen2 at equal width, heads, feed-forward arithmetic and layer runs",
+           "beside": ("vilepel at equal width, heads, head size, feed-forward sizes, reach and "
+                      "layers" if args.design == "pimidra" else
+                      "qwen2 at equal width, heads, feed-forward arithmetic and layer runs"),
            "dtype": "bfloat16", "data": "synthetic", "sizes": {}}
     layers = args.layers or 8
-    sizes = ZOLAPEL_SIZES if args.design == "zolapel" else DESIGN_SIZES
+    sizes = {"zolapel": ZOLAPEL_SIZES, "pimidra": PIMIDRA_SIZES}.get(args.design, DESIGN_SIZES)
     for name in (args.size.split(",") if args.size else sorted(sizes)):
         cfgs = design_configs(args.design, name, layers)
         width = sizes[name][0]
@@ -681,7 +727,7 @@ def main() -> int:
                     help="tokens a step of the long prompt in --scenario longctx (default 2,048)")
     ap.add_argument("--scenario", choices=SCENARIOS, default=None,
                     help="run a serving workload through the entry point instead of the benchmark")
-    ap.add_argument("--design", choices=["vilepel", "zolapel"], default=None,
+    ap.add_argument("--design", choices=["vilepel", "zolapel", "pimidra"], default=None,
                     help="measure another design beside Qwen2 at equal size instead of the benchmark")
     ap.add_argument("--size", default=None, help="with --design: sizes to run, e.g. s,m")
     args = ap.parse_args()
