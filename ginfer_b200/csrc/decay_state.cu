@@ -14,14 +14,18 @@
 //   gla_prepare_kernel        q * D^-1/2, k, v as fp32 and the decays sigmoid(z)^(1/tau) =
 //                             exp(log_sigmoid(z) / tau).
 //   decay_recurrence_kernel   a block a (request, head, tile of columns), token after token.  The
-//                             columns of S are independent: LP lanes share a column (DPER rows each,
-//                             in registers) and add their shares of o up by shuffles; the tokens'
-//                             operands come a chunk ahead through two stages of shared memory
-//                             (cp.async).  Lanes of a warp are laid out [LP][32 / LP columns], so
-//                             that a row of S is read and written in whole 32-byte sectors (LP = 4).
+//                             columns of S are independent: LP lanes share a column (DPER
+//                             neighbouring rows each, in registers) and add their shares of o up by
+//                             shuffles, four tokens' shares at a time, off the chain the next token
+//                             waits for; the tokens' operands come a chunk ahead through two stages
+//                             of shared memory (cp.async, 16 bytes a copy where rows are aligned)
+//                             and leave it four floats a load.  Lanes of a warp are laid out
+//                             [LP][32 / LP columns], so that a row of S is read and written in
+//                             whole 32-byte sectors (LP = 4).
 //   gated_norm_kernel         a warp a (token, group of channels): RMS norm with a gate, the gate
 //                             before the norm (y = o silu(z), then y / rms(y) w) or behind it
 //                             (o / rms(o) w silu(z)); the weight per channel or shared by the groups.
+//   gated_norm_block_kernel   the same with a block a (token, group), for groups over 512 channels.
 //
 // Everything here is fp32 arithmetic in both paths; only the projections that feed it and the
 // result of gated_norm_kernel have the activation dtype.
@@ -138,13 +142,22 @@ __device__ __forceinline__ void ds_copy4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src)
                : "memory");
 }
+__device__ __forceinline__ void ds_copy16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src)
+               : "memory");
+}
 __device__ __forceinline__ void ds_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void ds_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 constexpr int kDecayWarps = 4;
 constexpr int kDecayChunk = 8;
+constexpr int kGatedNormWarpMax = 512;           // channels a group one warp still norms
+constexpr int kDecayUnroll = 4;                    // tokens whose read-outs are reduced together
 
-template <int DPER, int LP>
+// A lane owns the DPER neighbouring rows lp * DPER .. of its column, so that the tokens' q, k and
+// decays come out of shared memory four at a time.  VEC: every operand row starts on a 16-byte
+// boundary and sizes are multiples of four, so the stages are filled by 16-byte copies.
+template <int DPER, int LP, bool VEC>
 __global__ void __launch_bounds__(kDecayWarps * 32)
 decay_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ k,
                         const float* __restrict__ v, const float* __restrict__ g,
@@ -155,17 +168,22 @@ decay_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ k
   constexpr int CW = 32 / LP;                      // columns a warp
   constexpr int VT = kDecayWarps * CW;             // columns a block
   constexpr int DP = DPER * LP;                    // key channels, padded
-  constexpr int ROW = 3 * DP + VT + 1;             // floats a token in a stage: q | k | g | v | c
-  extern __shared__ float stage[];                 // [2][kDecayChunk][ROW]
+  constexpr int ROW = 3 * DP + VT + 4;             // floats a token in a stage: q | k | g | v | c
+  constexpr int P = VEC ? 4 : 1;                   // floats a copy
+  extern __shared__ __align__(16) float stage[];   // [2][kDecayChunk][ROW]
   const int b = blockIdx.z, h = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int lp = lane / CW, vc = lane - lp * CW;
   const int col0 = blockIdx.x * VT;
   const int col = col0 + warp * CW + vc;
   const int D = dm.D, Vd = dm.Vd, gk = h / (dm.H / dm.G);
-  const bool live = col < Vd;
-  // the padding rows of the stages: q = k = 0 for ever (cp.async never writes there)
-  for (int i = threadIdx.x; i < 2 * kDecayChunk * ROW; i += blockDim.x) stage[i] = 0.f;
+  const bool live = col < Vd, perch = dm.gD != 1;
+  // what cp.async never writes stays zero for ever: the padding rows of q, k and the decays, and
+  // the columns past the last one
+  for (int i = threadIdx.x; i < 2 * kDecayChunk * ROW; i += blockDim.x) {
+    const int e = i % ROW;
+    if (e >= 3 * DP || (e % DP) >= D) stage[i] = 0.f;
+  }
   pdl_trigger();
   pdl_wait();
   const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
@@ -173,31 +191,72 @@ decay_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ k
   float s[DPER];
 #pragma unroll
   for (int i = 0; i < DPER; ++i) {
-    const int d = lp + LP * i;
+    const int d = lp * DPER + i;
     s[i] = (live && d < D) ? S[(size_t)d * Vd + col] : 0.f;
   }
   const float sk = skip != nullptr ? skip[h] : 0.f;
   __syncthreads();
 
-  auto fetch = [&](int chunk, int buf) {
+  auto copy = [&](float* dst, const float* src) {
+    if constexpr (VEC) ds_copy16(dst, src); else ds_copy4(dst, src);
+  };
+  const int dq = D / P, gq = perch ? dq : 0, per = 2 * dq + gq + VT / P;
+  auto fetch = [&](int chunk, int buf) {           // a warp a token, a lane a piece
     const int t0 = chunk * kDecayChunk;
     const int cnt = min(kDecayChunk, n - t0);
     float* base = stage + (size_t)buf * kDecayChunk * ROW;
-    const int per = 2 * D + dm.gD + VT + 1;
-    for (int i = threadIdx.x; i < cnt * per; i += blockDim.x) {
-      const int t = i / per, e = i - t * per;
+    for (int t = warp; t < cnt; t += kDecayWarps) {
       const size_t r = (size_t)(start + t0 + t);
       float* row = base + t * ROW;
-      if (e < D) ds_copy4(row + e, q + r * dm.ld_q + (size_t)gk * D + e);
-      else if (e < 2 * D) ds_copy4(row + DP + e - D, k + r * dm.ld_k + (size_t)gk * D + e - D);
-      else if (e < 2 * D + dm.gD)
-        ds_copy4(row + 2 * DP + e - 2 * D, g + r * dm.ld_g + (size_t)h * dm.gD + e - 2 * D);
-      else if (e < per - 1) {
-        const int cc = e - 2 * D - dm.gD;
-        if (col0 + cc < Vd) ds_copy4(row + 3 * DP + cc, v + r * dm.ld_v + (size_t)h * Vd + col0 + cc);
-      } else if (c != nullptr) ds_copy4(row + 3 * DP + VT, c + r * dm.ld_c + h);
+      for (int e = lane; e < per; e += 32) {
+        if (e < dq) copy(row + e * P, q + r * dm.ld_q + (size_t)gk * D + e * P);
+        else if (e < 2 * dq)
+          copy(row + DP + (e - dq) * P, k + r * dm.ld_k + (size_t)gk * D + (e - dq) * P);
+        else if (e < 2 * dq + gq)
+          copy(row + 2 * DP + (e - 2 * dq) * P, g + r * dm.ld_g + (size_t)h * D + (e - 2 * dq) * P);
+        else {
+          const int cc = (e - 2 * dq - gq) * P;
+          if (col0 + cc < Vd) copy(row + 3 * DP + cc, v + r * dm.ld_v + (size_t)h * Vd + col0 + cc);
+        }
+      }
+      if (lane == 0 && !perch) ds_copy4(row + 2 * DP, g + r * dm.ld_g + h);
+      if (lane == 1 && c != nullptr) ds_copy4(row + 3 * DP + VT, c + r * dm.ld_c + h);
     }
     ds_commit();
+  };
+
+  // one token: the state's rows of this lane move on, and the lane's share of the read-out
+  auto advance = [&](const float* row, float& vv) -> float {
+    vv = row[3 * DP + warp * CW + vc];
+    const float kv = (c != nullptr ? row[3 * DP + VT] : 1.f) * vv;
+    const float g1 = row[2 * DP];
+    const float* qr = row + lp * DPER;
+    float acc = 0.f;
+    if constexpr (DPER % 4 == 0) {
+#pragma unroll
+      for (int i = 0; i < DPER; i += 4) {
+        const float4 q4 = *reinterpret_cast<const float4*>(qr + i);
+        const float4 k4 = *reinterpret_cast<const float4*>(qr + DP + i);
+        const float4 g4 = perch ? *reinterpret_cast<const float4*>(qr + 2 * DP + i)
+                                : make_float4(g1, g1, g1, g1);
+        s[i] = fmaf(g4.x, s[i], k4.x * kv);
+        s[i + 1] = fmaf(g4.y, s[i + 1], k4.y * kv);
+        s[i + 2] = fmaf(g4.z, s[i + 2], k4.z * kv);
+        s[i + 3] = fmaf(g4.w, s[i + 3], k4.w * kv);
+        acc = fmaf(s[i], q4.x, acc);
+        acc = fmaf(s[i + 1], q4.y, acc);
+        acc = fmaf(s[i + 2], q4.z, acc);
+        acc = fmaf(s[i + 3], q4.w, acc);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < DPER; ++i) {
+        const float gd = perch ? qr[2 * DP + i] : g1;
+        s[i] = fmaf(gd, s[i], qr[DP + i] * kv);
+        acc = fmaf(s[i], qr[i], acc);
+      }
+    }
+    return acc;
   };
 
   const int chunks = (n + kDecayChunk - 1) / kDecayChunk;
@@ -208,28 +267,32 @@ decay_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ k
     if (ch + 1 < chunks) fetch(ch + 1, (ch + 1) & 1);
     const float* base = stage + (size_t)(ch & 1) * kDecayChunk * ROW;
     const int cnt = min(kDecayChunk, n - ch * kDecayChunk);
-    for (int t = 0; t < cnt; ++t) {
-      const float* row = base + t * ROW;
-      const float vv = row[3 * DP + warp * CW + vc];
-      const float kv = (c != nullptr ? row[3 * DP + VT] : 1.f) * vv;
-      const float g1 = row[2 * DP];
-      float acc = 0.f;
+    float* orow = o + (size_t)(start + ch * kDecayChunk) * ld_o + (size_t)h * Vd + col;
+    int t = 0;
+    for (; t + kDecayUnroll <= cnt; t += kDecayUnroll) {
+      float acc[kDecayUnroll], vv[kDecayUnroll];
 #pragma unroll
-      for (int i = 0; i < DPER; ++i) {
-        const int d = lp + LP * i;
-        const float gd = dm.gD == 1 ? g1 : row[2 * DP + d];
-        s[i] = fmaf(gd, s[i], row[DP + d] * kv);
-        acc = fmaf(s[i], row[d], acc);
-      }
+      for (int u = 0; u < kDecayUnroll; ++u) acc[u] = advance(base + (t + u) * ROW, vv[u]);
+#pragma unroll
+      for (int off = CW; off < 32; off <<= 1)
+#pragma unroll
+        for (int u = 0; u < kDecayUnroll; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], off);
+      if (lp == 0 && live)
+#pragma unroll
+        for (int u = 0; u < kDecayUnroll; ++u)
+          orow[(size_t)(t + u) * ld_o] = fmaf(sk, vv[u], acc[u]);
+    }
+    for (; t < cnt; ++t) {
+      float vv;
+      float acc = advance(base + t * ROW, vv);
 #pragma unroll
       for (int off = CW; off < 32; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-      if (lp == 0 && live)
-        o[(size_t)(start + ch * kDecayChunk + t) * ld_o + (size_t)h * Vd + col] = fmaf(sk, vv, acc);
+      if (lp == 0 && live) orow[(size_t)t * ld_o] = fmaf(sk, vv, acc);
     }
   }
 #pragma unroll
   for (int i = 0; i < DPER; ++i) {
-    const int d = lp + LP * i;
+    const int d = lp * DPER + i;
     if (live && d < D) S[(size_t)d * Vd + col] = s[i];
   }
 }
@@ -262,6 +325,41 @@ __global__ void gated_norm_kernel(const float* __restrict__ o, const G* __restri
   ss = warp_sum(ss);
   const float inv = 1.f / sqrtf(ss / (float)gs + eps);
   for (int j = lane; j < gs; j += 32) {
+    const float z = to_f32(grow[j]);
+    const float gz = z * ds_sigmoid(z);
+    const float wj = w[w_shared ? j : gi * gs + j];
+    const float y = gate_first ? orow[j] * gz * inv * wj : orow[j] * inv * wj * gz;
+    dst[j] = from_f32<T>(y);
+  }
+}
+
+
+// The same with a block a unit, for groups of thousands of channels (a warp would walk them alone).
+template <typename G, typename T>
+__global__ void __launch_bounds__(256)
+gated_norm_block_kernel(const float* __restrict__ o, const G* __restrict__ gate, int gate_ld,
+                        const float* __restrict__ w, int w_shared, int gate_first, float eps,
+                        T* __restrict__ out, int groups, int gs) {
+  __shared__ float scratch[33];
+  const int unit = blockIdx.x;
+  pdl_trigger();
+  pdl_wait();
+  const int r = unit / groups, gi = unit - r * groups;
+  const float* orow = o + (size_t)r * groups * gs + (size_t)gi * gs;
+  const G* grow = gate + (size_t)r * gate_ld + (size_t)gi * gs;
+  T* dst = out + (size_t)r * groups * gs + (size_t)gi * gs;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < gs; j += blockDim.x) {
+    float y = orow[j];
+    if (gate_first) {
+      const float z = to_f32(grow[j]);
+      y *= z * ds_sigmoid(z);
+    }
+    ss = fmaf(y, y, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)gs + eps);
+  for (int j = threadIdx.x; j < gs; j += blockDim.x) {
     const float z = to_f32(grow[j]);
     const float gz = z * ds_sigmoid(z);
     const float wj = w[w_shared ? j : gi * gs + j];
@@ -343,18 +441,26 @@ GF_EXPORT int gf_decay_recurrence(const float* q, int ld_q, const float* k, int 
   const int lp = wide ? 16 : 4;
   const int vt = kDecayWarps * (32 / lp);
   const dim3 grid((Vd + vt - 1) / vt, H, B), block(kDecayWarps * 32);
-#define GF_GO(DPER, LP)                                                                            \
-  if (lp == LP && D <= LP * DPER) {                                                                \
-    const size_t smem = (size_t)2 * kDecayChunk * (3 * LP * DPER + kDecayWarps * (32 / LP) + 1) *  \
+  auto aligned = [](const float* p, int ld) { return ((uintptr_t)p & 15) == 0 && ld % 4 == 0; };
+  const bool vec = D % 4 == 0 && Vd % 4 == 0 && aligned(q, ld_q) && aligned(k, ld_k) &&
+                   aligned(v, ld_v) && (gD == 1 || aligned(g, ld_g));
+#define GF_GO_V(DPER, LP, VEC)                                                                     \
+  {                                                                                                \
+    const size_t smem = (size_t)2 * kDecayChunk * (3 * LP * DPER + kDecayWarps * (32 / LP) + 4) *  \
                         sizeof(float);                                                             \
     static OncePerDevice once;                                                                     \
     const int rc = once.run([&] {                                                                  \
-      return cudaFuncSetAttribute(decay_recurrence_kernel<DPER, LP>,                               \
+      return cudaFuncSetAttribute(decay_recurrence_kernel<DPER, LP, VEC>,                          \
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
     });                                                                                            \
     if (rc) return rc;                                                                             \
-    return launch_kernel(decay_recurrence_kernel<DPER, LP>, grid, block, smem, st, q, k, v, g, c,  \
-                         skip, state, cu_seqlens, slot_ids, dm, o, ld_o);                          \
+    return launch_kernel(decay_recurrence_kernel<DPER, LP, VEC>, grid, block, smem, st, q, k, v,   \
+                         g, c, skip, state, cu_seqlens, slot_ids, dm, o, ld_o);                    \
+  }
+#define GF_GO(DPER, LP)                                                                            \
+  if (lp == LP && D <= LP * DPER) {                                                                \
+    if (vec) GF_GO_V(DPER, LP, true)                                                               \
+    GF_GO_V(DPER, LP, false)                                                                       \
   }
   GF_GO(4, 4)
   GF_GO(8, 4)
@@ -366,6 +472,7 @@ GF_EXPORT int gf_decay_recurrence(const float* q, int ld_q, const float* k, int 
   GF_GO(4, 16)
   GF_GO(8, 16)
   GF_GO(16, 16)
+#undef GF_GO_V
 #undef GF_GO
   return -3;
 }
@@ -378,12 +485,19 @@ GF_EXPORT int gf_gated_norm(const float* o, const void* gate, int gate_ld, int g
   if (units <= 0) return 0;
   auto st = (cudaStream_t)stream;
   const dim3 grid((units + 3) / 4), block(128);
+  const bool wide = gs > kGatedNormWarpMax;
 #define GF_GO(GT, OT)                                                                              \
-  return launch_kernel(gated_norm_kernel<GT, OT>, grid, block, 0, st, o, (const GT*)gate, gate_ld, \
-                       w, w_shared, gate_first, eps, (OT*)out, units, groups, gs)
-  if (gate_dtype == GF_F32 && dtype == GF_F32) GF_GO(float, float);
-  if (gate_dtype == GF_F32) GF_GO(float, bf);
-  if (dtype == GF_F32) GF_GO(bf, float);
-  GF_GO(bf, bf);
+  {                                                                                                \
+    if (wide)                                                                                      \
+      return launch_kernel(gated_norm_block_kernel<GT, OT>, dim3(units), dim3(256), 0, st, o,      \
+                           (const GT*)gate, gate_ld, w, w_shared, gate_first, eps, (OT*)out,       \
+                           groups, gs);                                                            \
+    return launch_kernel(gated_norm_kernel<GT, OT>, grid, block, 0, st, o, (const GT*)gate,        \
+                         gate_ld, w, w_shared, gate_first, eps, (OT*)out, units, groups, gs);      \
+  }
+  if (gate_dtype == GF_F32 && dtype == GF_F32) GF_GO(float, float)
+  if (gate_dtype == GF_F32) GF_GO(float, bf)
+  if (dtype == GF_F32) GF_GO(bf, float)
+  GF_GO(bf, bf)
 #undef GF_GO
 }

@@ -554,10 +554,11 @@ def test_convolution_step_sizes_and_the_slots_last_inputs(taps, cut):
 
 
 @pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
-def test_gated_norm_both_orders(act):
+@pytest.mark.parametrize("groups,gs", [(3, 20), (2, 520), (1, 1100)])   # a warp a group; a block
+def test_gated_norm_both_orders(act, groups, gs):
     from ginfer_b200.ops import decay
     g = torch.Generator(device="cuda").manual_seed(3)
-    T, groups, gs = 21, 3, 20
+    T = 21
     o = torch.randn(T, groups * gs, generator=g, device="cuda") * 2
     gate_wide = torch.randn(T, groups * gs + 8, generator=g, device="cuda")
     for gate in (gate_wide[:, 8:], gate_wide[:, 8:].to(act)):
