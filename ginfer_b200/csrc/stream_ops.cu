@@ -57,32 +57,6 @@ __global__ void outnorm_add_kernel(const float* __restrict__ x, const Y* __restr
 
 // The same with four channels an access and the row kept in registers (OPT quads a thread): per row
 // this moves what the definition needs and nothing else.  Needs H % 4 == 0 and H <= 4 * OPT * threads.
-template <typename T> struct Quad;
-template <> struct Quad<float> {
-  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
-    const float4 a = *reinterpret_cast<const float4*>(p);
-    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w;
-  }
-  static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
-    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-  }
-};
-template <> struct Quad<__nv_bfloat16> {
-  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4]) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(p);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
-    v[0] = a.x, v[1] = a.y, v[2] = b.x, v[3] = b.y;
-  }
-  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[4]) {
-    uint2 raw;
-    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
-    h[0] = __floats2bfloat162_rn(v[0], v[1]);
-    h[1] = __floats2bfloat162_rn(v[2], v[3]);
-    *reinterpret_cast<uint2*>(p) = raw;
-  }
-};
-
 template <typename Y, typename T, int OPT>
 __global__ void outnorm_add_vec_kernel(const float* __restrict__ x, const Y* __restrict__ y,
                                        const float* __restrict__ gamma, float eps,

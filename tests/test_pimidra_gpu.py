@@ -350,15 +350,18 @@ def test_router_weights_are_the_softmax_over_the_chosen_logits():
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh, nkv, D, Vd, rot", [(4, 2, 16, 16, 8), (3, 1, 12, 20, 0), (2, 2, 64, 64, 64),
-                                                 (5, 5, 24, 8, 6)])
+                                                 (5, 5, 24, 8, 6), (3, 1, 32, 24, 16), (2, 1, 10, 6, 4),
+                                                 (16, 4, 128, 128, 64)])
 def test_whole_projection_norm_rotation_mix_and_cache_write(dtype, nh, nkv, D, Vd, rot):
+    # sizes in multiples of four take the kernel with four channels an access (but the 16-channel
+    # heads, whose rows of values to mix in start anywhere), the others a channel a thread
     from ginfer_b200 import ops
     g = torch.Generator().manual_seed(D + rot)
     T, slots = 9, 40
     cols = (nh + nkv) * D + nkv * Vd
     ld = cols + (-cols % 8)
     qkv = (torch.randn(T, ld, generator=g) * 2).to(dtype)
-    vf = torch.randn(T, nkv * Vd + 3, generator=g).to(dtype)
+    vf = torch.randn(T, nkv * Vd + (3 if D == 16 else 4), generator=g).to(dtype)
     qw, kw = torch.rand(nh * D, generator=g) + 0.5, torch.rand(nkv * D, generator=g) + 0.5
     freqs = torch.rand(rot // 2, generator=g)
     pos = torch.randint(0, 900, (T,), generator=g).int()
@@ -554,7 +557,8 @@ def test_convolution_step_sizes_and_the_slots_last_inputs(taps, cut):
 
 
 @pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("groups,gs", [(3, 20), (2, 520), (1, 1100)])   # a warp a group; a block
+# a warp a group; a block a group with four channels an access, and with one
+@pytest.mark.parametrize("groups,gs", [(3, 20), (2, 520), (1, 1100), (2, 4096), (2, 522)])
 def test_gated_norm_both_orders(act, groups, gs):
     from ginfer_b200.ops import decay
     g = torch.Generator(device="cuda").manual_seed(3)
