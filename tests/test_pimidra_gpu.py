@@ -154,6 +154,21 @@ def test_cuts_agree_with_plain(tmp_path_factory, name, dtype):
                 assert float(np.abs(row - ref).max()) <= 1e-3 * scale, (cut, key)
 
 
+def test_a_long_portion_takes_the_tcgen05_grouped_products(tmp_path_factory):
+    """Six hundred tokens in one step are 1,200 (token, expert) pairs in the routed layers that
+    choose two experts: the grouped products run on tcgen05 (with the SiLU gate in the epilogue),
+    the long portion takes the recurrence with sixteen lanes a column, and the norm behind the sum
+    adds up the pairs' rows; a short request follows it."""
+    from ginfer_b200.ops import moe
+    cfg = tp.MIXED
+    d = folder(tmp_path_factory, "MIXED", cfg, "bfloat16")
+    reqs = prompts(cfg["vocab"], [600, 70], seed=12)
+    assert 600 * 2 >= moe.TCGEN05_MIN_PAIRS
+    steps = replay.cut_whole(reqs)
+    rows = replay.run_in_process(make_runner(d, "bfloat16", replay.peak_tokens(steps)), steps)
+    check(rows, expected(d, cfg, reqs), "bfloat16", reqs)
+
+
 @pytest.mark.parametrize("name, dtype", [("MIXED", "float32"), ("WIDE", "bfloat16")])
 def test_long_decoding_past_chunks_and_pages_through_graphs(tmp_path_factory, name, dtype):
     cfg = getattr(tp, name)
