@@ -55,8 +55,12 @@ def gla_prepare(proj: torch.Tensor, z: torch.Tensor, HD: int, HV: int, q_scale: 
     return out
 
 
-# Requests x heads x column tiles below this leave most of the GPU idle with four lanes a column.
-WIDE_BELOW_BLOCKS = 2 * 148
+# With fewer blocks of four lanes a column than this (requests x heads x tiles of 32 columns), long
+# portions take sixteen lanes a column: four times the blocks, each with a shorter chain a token.
+# Measured on a B200 with 2,048-token portions and key sizes 64 and 128: sixteen lanes win up to 64
+# such blocks (430 against 605 us at 32, 540 against 605 us at 64), are level at 96 and lose from
+# 128 on (710 against 605 us), where four lanes a column already give every SM a block.
+WIDE_BELOW_BLOCKS = 96
 WIDE_MIN_TOKENS = 64
 
 
