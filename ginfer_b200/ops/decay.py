@@ -55,6 +55,9 @@ def gla_prepare(proj: torch.Tensor, z: torch.Tensor, HD: int, HV: int, q_scale: 
     return out
 
 
+# The recurrence keeps a column's rows of the state in registers: key sizes up to this.
+MAX_KEY_SIZE = 256
+
 # With fewer blocks of four lanes a column than this (requests x heads x tiles of 32 columns), long
 # portions take sixteen lanes a column: four times the blocks, each with a shorter chain a token.
 # Measured on a B200 with 2,048-token portions and key sizes 64 and 128: sixteen lanes win up to 64

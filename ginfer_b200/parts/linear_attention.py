@@ -26,6 +26,9 @@ class GatedLinearAttention(Mixer):
         self.D, self.Vd, self.tau = int(key_dim), int(v_dim), float(tau)
         if not (self.tau > 0):
             raise ValueError(f"tau must be > 0, got {tau}")
+        if self.D > decay.MAX_KEY_SIZE:
+            raise ValueError(f"a key size of {self.D} is over the recurrence kernel's "
+                             f"{decay.MAX_KEY_SIZE}")
         self.eps, self.decay_rank = float(norm_eps), int(decay_rank)     # -1: the file's
         self.prefix = prefix + "." if prefix else ""
 

@@ -37,6 +37,9 @@ class StateSpaceDual(Mixer):
                              "equal parts")
         if self.taps < 1:
             raise ValueError("the convolution needs at least one tap")
+        if self.N > decay.MAX_KEY_SIZE:
+            raise ValueError(f"a state size of {self.N} is over the recurrence kernel's "
+                             f"{decay.MAX_KEY_SIZE}")
         self.channels = self.inner + 2 * self.G * self.N
         self.state_floats = self.H * self.N * self.Vd
         self.prefix = prefix + "." if prefix else ""

@@ -101,6 +101,15 @@ def test_refusals(edit, text):
         build(cfg)
 
 
+def test_key_sizes_over_the_recurrences_limit_are_refused_when_the_model_is_built():
+    for i, key in ((1, "state"), (2, "dim")):
+        cfg = copy.deepcopy(tp.MIXED)
+        cfg["layers"][i]["mixer"][key] = 257
+        arch, typed = build(cfg)
+        with pytest.raises(ValueError, match="recurrence kernel"):
+            DecoderModel(arch.build_plan(typed))
+
+
 def test_mask_span_encoding():
     from ginfer_b200.ops import mask_span
     assert (mask_span(), mask_span(window=7), mask_span(chunk=5)) == (0, 7, -5)
