@@ -6,7 +6,8 @@
 // Keys have hd channels, values vd (the two may differ).  Keys are visited in order in
 // groups of 32 starting at lo, so a row's result depends only on (lo, p) and the cache contents,
 // never on how the step was cut or what else is in the batch.  Running maximum, sum and the output
-// accumulator are fp32.
+// accumulator are fp32.  Two optional shapings of a score s = q.k * scale, in this order: a soft cap
+// (s <- cap * tanh(s / cap)) and a distance bias a head (s <- s - slope_n * (p - c)).
 #include "common.cuh"
 
 namespace gf {
@@ -19,7 +20,8 @@ __global__ void paged_attention_simt_kernel(
     const T* __restrict__ q, int q_row_stride, const T* __restrict__ kpages,
     const T* __restrict__ vpages, const int* __restrict__ block_table, int table_stride,
     const int* __restrict__ seq_of_token, const int* __restrict__ positions, T* __restrict__ out,
-    int num_pairs, int nh, int nkv, int hd, int vd, int page_size, int window, float scale) {
+    int num_pairs, int nh, int nkv, int hd, int vd, int page_size, int window, float scale,
+    float softcap, const float* __restrict__ slopes) {
   extern __shared__ float qs_all[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pair = blockIdx.x * kWarps + warp;
@@ -30,6 +32,7 @@ __global__ void paged_attention_simt_kernel(
   const int b = seq_of_token[t];
   const int p = positions[t];
   const int lo = first_visible_key(p, window);
+  const float slope = slopes ? slopes[n] : 0.f;
   const int* tbl = block_table + (size_t)b * table_stride;
   const T* qrow = q + (size_t)t * q_row_stride + (size_t)n * hd;
   for (int d = lane; d < hd; d += 32) qs[d] = to_f32(qrow[d]);
@@ -53,6 +56,8 @@ __global__ void paged_attention_simt_kernel(
       float dot = 0.f;
       for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_f32(krow[d]), dot);
       s = dot * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+      s -= slope * (float)(p - c);
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float pexp = valid ? expf(s - m_new) : 0.f;
@@ -90,12 +95,14 @@ GF_DEFINE_PDL_SWITCH
 
 // q: rows of q_row_stride elements whose first nh*hd hold the query heads.  kpages/vpages:
 // [num_pages, page_size, nkv, hd] and [.., nkv, vd].  out: [T, nh, vd] packed.  window: the mask as
-// first_visible_key() reads it.  Returns -3 for head sizes it refuses.
+// first_visible_key() reads it.  softcap <= 0: no cap; slopes: nh fp32 slopes or null.  Returns -3
+// for head sizes it refuses.
 GF_EXPORT int gf_paged_attention_simt(const void* q, int q_row_stride, const void* kpages,
                                       const void* vpages, const int* block_table, int table_stride,
                                       const int* seq_of_token, const int* positions, void* out,
                                       int T, int nh, int nkv, int hd, int vd, int page_size,
-                                      int window, float scale, int dtype, void* stream) {
+                                      int window, float scale, float softcap, const float* slopes,
+                                      int dtype, void* stream) {
   if (T <= 0) return 0;
   if (hd > kMaxHeadDim || hd <= 0 || vd > kMaxHeadDim || vd <= 0 || nh % nkv) return -3;
   const int pairs = T * nh;
@@ -106,11 +113,11 @@ GF_EXPORT int gf_paged_attention_simt(const void* q, int q_row_stride, const voi
     paged_attention_simt_kernel<float><<<blocks, kWarps * 32, smem, st>>>(
         (const float*)q, q_row_stride, (const float*)kpages, (const float*)vpages, block_table,
         table_stride, seq_of_token, positions, (float*)out, pairs, nh, nkv, hd, vd, page_size,
-        window, scale);
+        window, scale, softcap, slopes);
   else
     paged_attention_simt_kernel<__nv_bfloat16><<<blocks, kWarps * 32, smem, st>>>(
         (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)kpages,
         (const __nv_bfloat16*)vpages, block_table, table_stride, seq_of_token, positions,
-        (__nv_bfloat16*)out, pairs, nh, nkv, hd, vd, page_size, window, scale);
+        (__nv_bfloat16*)out, pairs, nh, nkv, hd, vd, page_size, window, scale, softcap, slopes);
   return launch_status();
 }

@@ -38,6 +38,11 @@ using bf = __nv_bfloat16;
 
 __device__ __forceinline__ float ds_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float ds_sigmoid(float x) { return 1.f / (1.f + expf(-x)); }
+// The gate of a gated norm: z * sigmoid(z) (SiLU), or sigmoid(z) alone.
+__device__ __forceinline__ float ds_gate(float z, int sigmoid_only) {
+  const float sg = ds_sigmoid(z);
+  return sigmoid_only ? sg : z * sg;
+}
 __device__ __forceinline__ float ds_log_sigmoid(float x) {
   return fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
 }
@@ -129,6 +134,20 @@ __global__ void gla_prepare_kernel(const T* __restrict__ proj, int ld, const flo
   else if (c < 3 * HD) y = expf(ds_log_sigmoid(z[(size_t)r * HD + c - 2 * HD]) * inv_tau);
   else y = to_f32(proj[(size_t)r * ld + c - HD]);
   out[i] = y;
+}
+
+// out[r, c] = silu(proj[r, c]) in fp32 for the first `width` columns of a projection row: the q, k
+// and v of a linear attention whose operands pass an activation and no other preparation.
+template <typename T>
+__global__ void silu_f32_kernel(const T* __restrict__ proj, int ld, int rows, int width,
+                                float* __restrict__ out) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_trigger();
+  pdl_wait();
+  if (i >= (size_t)rows * width) return;
+  const int r = (int)(i / width), c = (int)(i - (size_t)r * width);
+  const float z = to_f32(proj[(size_t)r * ld + c]);
+  out[i] = z * ds_sigmoid(z);
 }
 
 // ------------------------------------------------------------------------------- the recurrence
@@ -304,9 +323,10 @@ decay_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ k
 template <typename G, typename T>
 __global__ void gated_norm_kernel(const float* __restrict__ o, const G* __restrict__ gate,
                                   int gate_ld, const float* __restrict__ w, int w_shared,
-                                  int gate_first, float eps, T* __restrict__ out, int units,
+                                  int gate_mode, float eps, T* __restrict__ out, int units,
                                   int groups, int gs) {
   const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  const int sig = gate_mode >> 1, gate_first = gate_mode & 1;
   pdl_trigger();
   pdl_wait();
   if (unit >= units) return;
@@ -319,7 +339,7 @@ __global__ void gated_norm_kernel(const float* __restrict__ o, const G* __restri
     float y = orow[j];
     if (gate_first) {
       const float z = to_f32(grow[j]);
-      y *= z * ds_sigmoid(z);
+      y *= ds_gate(z, sig);
     }
     ss = fmaf(y, y, ss);
   }
@@ -327,7 +347,7 @@ __global__ void gated_norm_kernel(const float* __restrict__ o, const G* __restri
   const float inv = 1.f / sqrtf(ss / (float)gs + eps);
   for (int j = lane; j < gs; j += 32) {
     const float z = to_f32(grow[j]);
-    const float gz = z * ds_sigmoid(z);
+    const float gz = ds_gate(z, sig);
     const float wj = w[w_shared ? j : gi * gs + j];
     const float y = gate_first ? orow[j] * gz * inv * wj : orow[j] * inv * wj * gz;
     dst[j] = from_f32<T>(y);
@@ -339,10 +359,11 @@ __global__ void gated_norm_kernel(const float* __restrict__ o, const G* __restri
 template <typename G, typename T>
 __global__ void __launch_bounds__(256)
 gated_norm_block_kernel(const float* __restrict__ o, const G* __restrict__ gate, int gate_ld,
-                        const float* __restrict__ w, int w_shared, int gate_first, float eps,
+                        const float* __restrict__ w, int w_shared, int gate_mode, float eps,
                         T* __restrict__ out, int groups, int gs) {
   __shared__ float scratch[33];
   const int unit = blockIdx.x;
+  const int sig = gate_mode >> 1, gate_first = gate_mode & 1;
   pdl_trigger();
   pdl_wait();
   const int r = unit / groups, gi = unit - r * groups;
@@ -354,7 +375,7 @@ gated_norm_block_kernel(const float* __restrict__ o, const G* __restrict__ gate,
     float y = orow[j];
     if (gate_first) {
       const float z = to_f32(grow[j]);
-      y *= z * ds_sigmoid(z);
+      y *= ds_gate(z, sig);
     }
     ss = fmaf(y, y, ss);
   }
@@ -362,7 +383,7 @@ gated_norm_block_kernel(const float* __restrict__ o, const G* __restrict__ gate,
   const float inv = 1.f / sqrtf(ss / (float)gs + eps);
   for (int j = threadIdx.x; j < gs; j += blockDim.x) {
     const float z = to_f32(grow[j]);
-    const float gz = z * ds_sigmoid(z);
+    const float gz = ds_gate(z, sig);
     const float wj = w[w_shared ? j : gi * gs + j];
     const float y = gate_first ? orow[j] * gz * inv * wj : orow[j] * inv * wj * gz;
     dst[j] = from_f32<T>(y);
@@ -375,10 +396,11 @@ gated_norm_block_kernel(const float* __restrict__ o, const G* __restrict__ gate,
 template <typename G, typename T>
 __global__ void __launch_bounds__(1024)
 gated_norm_vec_kernel(const float* __restrict__ o, const G* __restrict__ gate, int gate_ld,
-                      const float* __restrict__ w, int w_shared, int gate_first, float eps,
+                      const float* __restrict__ w, int w_shared, int gate_mode, float eps,
                       T* __restrict__ out, int groups, int gs) {
   __shared__ float scratch[33];
   const int unit = blockIdx.x, nq = gs >> 2;
+  const int sig = gate_mode >> 1, gate_first = gate_mode & 1;
   pdl_trigger();
   pdl_wait();
   const int r = unit / groups, gi = unit - r * groups;
@@ -394,7 +416,7 @@ gated_norm_vec_kernel(const float* __restrict__ o, const G* __restrict__ gate, i
       float z[4];
       Quad<G>::load(grow + 4 * q, z);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) y[u] *= z[u] * ds_sigmoid(z[u]);
+      for (int u = 0; u < 4; ++u) y[u] *= ds_gate(z[u], sig);
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) ss = fmaf(y[u], y[u], ss);
@@ -408,7 +430,7 @@ gated_norm_vec_kernel(const float* __restrict__ o, const G* __restrict__ gate, i
     Quad<float>::load(wrow + 4 * q, wq);
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const float gz = z[u] * ds_sigmoid(z[u]);
+      const float gz = ds_gate(z[u], sig);
       y[u] = gate_first ? y[u] * gz * inv * wq[u] : y[u] * inv * wq[u] * gz;
     }
     Quad<T>::store(dst + 4 * q, y);
@@ -468,6 +490,18 @@ GF_EXPORT int gf_gla_prepare(const void* proj, int ld, const float* z, int T, in
                        HV, q_scale, inv_tau, out);
 }
 
+GF_EXPORT int gf_silu_f32(const void* proj, int ld, int T, int width, float* out, int dtype,
+                          void* stream) {
+  if (T <= 0 || width <= 0) return 0;
+  const size_t total = (size_t)T * width;
+  const dim3 grid((unsigned)((total + 255) / 256)), block(256);
+  auto st = (cudaStream_t)stream;
+  if (dtype == GF_F32)
+    return launch_kernel(silu_f32_kernel<float>, grid, block, 0, st, (const float*)proj, ld, T,
+                         width, out);
+  return launch_kernel(silu_f32_kernel<bf>, grid, block, 0, st, (const bf*)proj, ld, T, width, out);
+}
+
 // q, k: rows of G heads of D; v: rows of H heads of Vd; g: rows of H x gD decays (gD = D or 1);
 // c: rows of H factors on k, or null; skip: H weights of v in the output, or null; state: the
 // slots, S [H, D, Vd] first in each.  wide: sixteen lanes a column instead of four (few requests
@@ -525,6 +559,7 @@ GF_EXPORT int gf_decay_recurrence(const float* q, int ld_q, const float* k, int 
 }
 
 // o: [T, groups * gs] fp32 -> out in the activation dtype.  gate_dtype: the gate's own.
+// gate_first: bit 0 = the gate before the norm; bit 1 = the gate is sigmoid(z), not z sigmoid(z).
 GF_EXPORT int gf_gated_norm(const float* o, const void* gate, int gate_ld, int gate_dtype,
                             const float* w, int w_shared, int gate_first, float eps, void* out,
                             int T, int groups, int gs, int dtype, void* stream) {

@@ -311,6 +311,30 @@ int launch_add_rmsnorm(const void* x, const void* delta, const void* gamma, cons
                        (const G*)gamma, rows, (float*)sum_out, (T*)normed, H, eps);
 }
 
+// Element-wise activations in place, fp32 arithmetic: kind 0 = relu(x)^2; kind 1 = a soft cap,
+// c * tanh(x / c).  Four elements a pass where the count allows, the rest one by one.
+template <typename T>
+__global__ void activation_kernel(T* __restrict__ x, size_t total, int kind, float c) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t nq = (((uintptr_t)x % (4 * sizeof(T))) == 0) ? total / 4 : 0;
+  auto f = [&](float v) {
+    if (kind == 0) { v = fmaxf(v, 0.f); return v * v; }
+    return c * tanhf(v / c);
+  };
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nq;
+       i += (size_t)gridDim.x * blockDim.x) {
+    float v[4];
+    Quad<T>::load(x + 4 * i, v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = f(v[k]);
+    Quad<T>::store(x + 4 * i, v);
+  }
+  for (size_t i = 4 * nq + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x)
+    x[i] = from_f32<T>(f(to_f32(x[i])));
+}
+
 }  // namespace gf
 
 using namespace gf;
@@ -404,4 +428,18 @@ GF_EXPORT int gf_silu_mul(const void* gu, void* out, int T, int I, int dtype, vo
                          (float*)out, total);
   return launch_kernel(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, st,
                        (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total);
+}
+
+// x: total elements of `dtype`, changed in place.  kind 0: relu(x)^2; kind 1: c * tanh(x / c).
+GF_EXPORT int gf_activation(void* x, long long total, int kind, float c, int dtype, void* stream) {
+  if (total <= 0) return 0;
+  if (kind < 0 || kind > 1 || (kind == 1 && !(c > 0.f))) return -3;
+  auto st = (cudaStream_t)stream;
+  const size_t want = ((size_t)total / 4 + 255) / 256 + 1;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  if (dtype == GF_F32)
+    return launch_kernel(activation_kernel<float>, dim3(blocks), dim3(256), 0, st, (float*)x,
+                         (size_t)total, kind, c);
+  return launch_kernel(activation_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, st,
+                       (__nv_bfloat16*)x, (size_t)total, kind, c);
 }

@@ -78,6 +78,45 @@ __global__ void latent_prepare_kernel(const T* __restrict__ qd, int ld, int H, i
   }
 }
 
+// A token's two latent vectors out of one projection row: the query latent (Q channels from q_col,
+// RMS-normed with qw into cq, in the activation type, for the query up-projection) and the key/value
+// latent (C channels from c_col, RMS-normed with cw into the token's cache slot).  Either may be
+// absent (Q = 0; slot_mapping null).  One block a token.
+template <typename T>
+__global__ void latent_norms_kernel(const T* __restrict__ proj, int ld, int q_col, int Q,
+                                    const float* __restrict__ qw, T* __restrict__ cq, int c_col,
+                                    int C, const float* __restrict__ cw, float eps,
+                                    const int* __restrict__ slot_mapping, T* __restrict__ c_pages) {
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  pdl_trigger();
+  pdl_wait();
+  const T* row = proj + (size_t)t * ld;
+  if (Q > 0) {
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < Q; j += blockDim.x) {
+      const float v = to_f32(row[q_col + j]);
+      ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float rms = sqrtf(ss / (float)Q + eps);
+    for (int j = threadIdx.x; j < Q; j += blockDim.x)
+      cq[(size_t)t * Q + j] = from_f32<T>(to_f32(row[q_col + j]) / rms * qw[j]);
+  }
+  if (slot_mapping != nullptr && C > 0) {
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < C; j += blockDim.x) {
+      const float v = to_f32(row[c_col + j]);
+      ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float rms = sqrtf(ss / (float)C + eps);
+    T* dst = c_pages + (size_t)slot_mapping[t] * C;
+    for (int j = threadIdx.x; j < C; j += blockDim.x)
+      dst[j] = from_f32<T>(to_f32(row[c_col + j]) / rms * cw[j]);
+  }
+}
+
 template <typename T>
 __global__ void latent_attention_kernel(const float* __restrict__ q_lat,   // [H, T, C]
                                         const float* __restrict__ q_rot,   // [T, H, R]
@@ -493,6 +532,22 @@ GF_EXPORT int gf_latent_prepare(const void* qd, int ld, int H, int D, int R, int
   return launch_kernel(latent_prepare_kernel<bf>, dim3(T), dim3(128), 0, st, (const bf*)qd, ld, H,
                        D, R, C, rot, freq, cnorm_w, eps, positions, slot_mapping, (bf*)c_pages,
                        (bf*)r_pages, q_rot);
+}
+
+GF_EXPORT int gf_latent_norms(const void* proj, int ld, int q_col, int Q, const float* qw, void* cq,
+                              int c_col, int C, const float* cw, float eps,
+                              const int* slot_mapping, void* c_pages, int T, int dtype,
+                              void* stream) {
+  if (T <= 0) return 0;
+  auto st = (cudaStream_t)stream;
+  const int widest = Q > C ? Q : C;
+  const dim3 grid(T), block(widest > 512 ? 256 : 128);
+  if (dtype == GF_F32)
+    return launch_kernel(latent_norms_kernel<float>, grid, block, 0, st, (const float*)proj, ld,
+                         q_col, Q, qw, (float*)cq, c_col, C, cw, eps, slot_mapping,
+                         (float*)c_pages);
+  return launch_kernel(latent_norms_kernel<bf>, grid, block, 0, st, (const bf*)proj, ld, q_col, Q,
+                       qw, (bf*)cq, c_col, C, cw, eps, slot_mapping, (bf*)c_pages);
 }
 
 GF_EXPORT int gf_latent_attention(const float* q_lat, const float* q_rot, const void* c_pages,

@@ -209,11 +209,18 @@ __global__ void stream_update_vec_kernel(const float* __restrict__ x, const int*
 // are the keys as projected).  freqs[n_pairs]; pair i of a head is channels (2i, 2i + 1) if
 // interleaved, else (i, i + n_pairs); channels from 2 n_pairs on pass unrotated.  qw / kw: norm
 // weights of hd channels, or null for no norm.  slot_mapping null: nothing is cached.
+// A factor on the queries that grows with the position: 1 + coef * ln(floor((p + 1) / every) + 1);
+// every <= 0: none.
+__device__ __forceinline__ float query_temperature(int p, float coef, int every) {
+  return every > 0 ? 1.f + coef * logf((float)((p + 1) / every) + 1.f) : 1.f;
+}
+
 template <typename T>
 __global__ void qk_norm_rope_kernel(T* __restrict__ qkv, int stride, int num_tokens, int nh,
                                     int nkv, int hd, int k_off, int v_off,
                                     const float* __restrict__ qw, const float* __restrict__ kw,
-                                    float eps, const float* __restrict__ freqs, int n_pairs,
+                                    float eps, float qt_coef, int qt_every,
+                                    const float* __restrict__ freqs, int n_pairs,
                                     int interleaved, const int* __restrict__ positions,
                                     const int* __restrict__ slot_mapping, T* __restrict__ kpages,
                                     T* __restrict__ vpages) {
@@ -246,10 +253,12 @@ __global__ void qk_norm_rope_kernel(T* __restrict__ qkv, int stride, int num_tok
     inv = 1.f / sqrtf(ss / (float)hd + eps);
   }
   const float pos = (float)positions[t];
+  const float tq = is_k ? 1.f : query_temperature(positions[t], qt_coef, qt_every);
   for (int i = lane; i < n_pairs; i += 32) {
     const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + n_pairs;
     float u = to_f32(src[a]) * inv, v = to_f32(src[b]) * inv;
     if (w) u *= w[a], v *= w[b];
+    u *= tq, v *= tq;
     float sn, cs;
     sincosf(pos * freqs[i], &sn, &cs);
     dst[a] = from_f32<T>(u * cs - v * sn);
@@ -258,7 +267,7 @@ __global__ void qk_norm_rope_kernel(T* __restrict__ qkv, int stride, int num_tok
   for (int c = 2 * n_pairs + lane; c < hd; c += 32) {
     float u = to_f32(src[c]) * inv;
     if (w) u *= w[c];
-    dst[c] = from_f32<T>(u);
+    dst[c] = from_f32<T>(u * tq);
   }
 }
 
@@ -270,7 +279,8 @@ template <typename T>
 __global__ void qk_norm_rope_vec_kernel(T* __restrict__ qkv, int stride, int num_tokens, int nh,
                                         int nkv, int hd, int k_off, int v_off,
                                         const float* __restrict__ qw, const float* __restrict__ kw,
-                                        float eps, const float* __restrict__ freqs, int n_pairs,
+                                        float eps, float qt_coef, int qt_every,
+                                        const float* __restrict__ freqs, int n_pairs,
                                         const int* __restrict__ positions,
                                         const int* __restrict__ slot_mapping,
                                         T* __restrict__ kpages, T* __restrict__ vpages) {
@@ -320,6 +330,11 @@ __global__ void qk_norm_rope_vec_kernel(T* __restrict__ qkv, int stride, int num
     Quad<float>::load(w + c, wv);
 #pragma unroll
     for (int i = 0; i < 4; ++i) x[i] = x[i] * inv * wv[i];
+  }
+  if (!is_k && qt_every > 0) {
+    const float tq = query_temperature(positions[t], qt_coef, qt_every);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x[i] *= tq;
   }
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -459,6 +474,7 @@ GF_EXPORT int gf_stream_update(const float* x, const int* rows, const void* y, i
 
 GF_EXPORT int gf_qk_norm_rope(void* qkv, int stride, int T, int nh, int nkv, int hd, int k_off,
                               int v_off, const float* qw, const float* kw, float eps,
+                              float qt_coef, int qt_every,
                               const float* freqs, int n_pairs, int interleaved,
                               const int* positions, const int* slot_mapping, void* kpages,
                               void* vpages, int dtype, void* stream) {
@@ -479,18 +495,18 @@ GF_EXPORT int gf_qk_norm_rope(void* qkv, int stride, int T, int nh, int nkv, int
     const size_t smem = 2 * (size_t)n_pairs * sizeof(float);
     if (dtype == GF_F32)
       return launch_kernel(qk_norm_rope_vec_kernel<float>, grid, block, smem, st, (float*)qkv, stride,
-                           T, nh, nkv, hd, k_off, v_off, qw, kw, eps, freqs, n_pairs, positions,
+                           T, nh, nkv, hd, k_off, v_off, qw, kw, eps, qt_coef, qt_every, freqs, n_pairs, positions,
                            slot_mapping, (float*)kpages, (float*)vpages);
     return launch_kernel(qk_norm_rope_vec_kernel<bf>, grid, block, smem, st, (bf*)qkv, stride, T, nh,
-                         nkv, hd, k_off, v_off, qw, kw, eps, freqs, n_pairs, positions,
+                         nkv, hd, k_off, v_off, qw, kw, eps, qt_coef, qt_every, freqs, n_pairs, positions,
                          slot_mapping, (bf*)kpages, (bf*)vpages);
   }
   if (dtype == GF_F32)
     return launch_kernel(qk_norm_rope_kernel<float>, grid, block, 0, st, (float*)qkv, stride, T,
-                         nh, nkv, hd, k_off, v_off, qw, kw, eps, freqs, n_pairs, interleaved,
+                         nh, nkv, hd, k_off, v_off, qw, kw, eps, qt_coef, qt_every, freqs, n_pairs, interleaved,
                          positions, slot_mapping, (float*)kpages, (float*)vpages);
   return launch_kernel(qk_norm_rope_kernel<bf>, grid, block, 0, st, (bf*)qkv, stride, T, nh, nkv,
-                       hd, k_off, v_off, qw, kw, eps, freqs, n_pairs, interleaved, positions,
+                       hd, k_off, v_off, qw, kw, eps, qt_coef, qt_every, freqs, n_pairs, interleaved, positions,
                        slot_mapping, (bf*)kpages, (bf*)vpages);
 }
 

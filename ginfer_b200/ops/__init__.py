@@ -7,7 +7,7 @@ tensor that is not on a CUDA device is an error, and so is a library that cannot
 """
 from __future__ import annotations
 
-from ctypes import c_float, c_int, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
@@ -278,6 +278,20 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def activation_(x: torch.Tensor, kind: str, c: float = 0.0) -> torch.Tensor:
+    """In place, fp32 arithmetic: ``kind`` ``"relu2"``: ``relu(x)^2``; ``"softcap"``:
+    ``c * tanh(x / c)``."""
+    _cuda(x)
+    assert x.is_contiguous()
+    f = _fn("elementwise", "gf_activation",
+            [c_void_p, c_longlong, c_int, c_float, c_int, c_void_p])
+    rc = f(_p(x), x.numel(), {"relu2": 0, "softcap": 1}[kind], float(c), _code(x.dtype), _stream())
+    if rc == -3:
+        raise ValueError(f"activation {kind!r} with constant {c}")
+    _ok(rc, "activation")
+    return x
+
+
 # ----------------------------------------------------------------------------- attention
 def mask_span(window: int = 0, chunk: int = 0) -> int:
     """How the attention kernels are told their mask, as one integer: 0 = every earlier key,
@@ -289,19 +303,25 @@ def mask_span(window: int = 0, chunk: int = 0) -> int:
 
 
 def paged_attention_simt(qkv, pages, block_table, seq_of_token, positions, nh, nkv, hd, scale,
-                         window, page_size, vd=None):
+                         window, page_size, vd=None, softcap: float = 0.0, slopes=None):
     """``window``: the mask as :func:`mask_span` gives it.  ``vd``: the values' head size where
-    it is not the keys' (``pages`` is then a pair of tensors)."""
-    _cuda(qkv, pages[0], pages[1], block_table, seq_of_token, positions)
+    it is not the keys' (``pages`` is then a pair of tensors).  ``softcap`` > 0: scores pass
+    ``cap * tanh(s / cap)``; ``slopes`` (fp32, a head): ``slope * (p - c)`` is taken off the score
+    of the key at ``c`` for the query at ``p``, after the cap."""
+    _cuda(qkv, pages[0], pages[1], block_table, seq_of_token, positions, slopes)
+    assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == nh
+                              and slopes.is_contiguous())
     T = qkv.shape[0]
     vd = hd if vd is None else int(vd)
     out = torch.empty((T, nh * vd), dtype=qkv.dtype, device=qkv.device)
     f = _fn("attention_simt", "gf_paged_attention_simt",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_int,
+             c_void_p])
     rc = f(_p(qkv), qkv.stride(0), _p(pages[0]), _p(pages[1]), _p(block_table),
            block_table.stride(0), _p(seq_of_token), _p(positions), _p(out), T, nh, nkv, hd, vd,
-           page_size, int(window), float(scale), _code(qkv.dtype), _stream())
+           page_size, int(window), float(scale), float(softcap or 0.0), _p(slopes),
+           _code(qkv.dtype), _stream())
     if rc == -3:
         raise ValueError(f"attention kernels take head sizes up to 256 and head counts that are "
                          f"a multiple of the kv head count; got head_dim={hd}, heads={nh}, "
@@ -319,26 +339,30 @@ def attention_fuses_rope(qkv: torch.Tensor, ctx, nh: int, nkv: int, hd: int) -> 
 
 def paged_attention(qkv: torch.Tensor, pages, block_table: torch.Tensor, ctx,
                     nh: int, nkv: int, hd: int, scale: float, window: int, page_size: int,
-                    rope=None, vd: int | None = None) -> torch.Tensor:
+                    rope=None, vd: int | None = None, softcap: float = 0.0,
+                    slopes=None) -> torch.Tensor:
     """Attention of the step's queries (first ``nh * hd`` columns of ``qkv``) over the paged
     cache; returns ``[T, nh * hd]``.  Picks the kernel by dtype, head size and batch shape.
     ``rope = (table or None, rotary_dim, write)`` where :func:`attention_fuses_rope`: q and k are
     still unrotated and the new k and v not yet in the cache.  ``window``: the mask as
     :func:`mask_span` gives it.  ``vd``: the values' head size if it differs from ``hd``
-    (``pages`` is then the pair of the cache's two planes; the result is ``[T, nh * vd]``)."""
+    (``pages`` is then the pair of the cache's two planes; the result is ``[T, nh * vd]``).
+    ``softcap``, ``slopes``: a soft cap on the scores and a distance bias a head, see
+    :func:`paged_attention_simt`."""
     from . import attention_bf16
+    shaped = dict(softcap=float(softcap or 0.0), slopes=slopes)
     if vd is not None and vd != hd:        # keys and values of different widths: the plain kernel
         assert rope is None
         return paged_attention_simt(qkv, pages, block_table, ctx.seq_of_token, ctx.positions, nh,
-                                    nkv, hd, scale, window, page_size, vd=vd)
+                                    nkv, hd, scale, window, page_size, vd=vd, **shaped)
     if qkv.dtype == torch.bfloat16:
         out = attention_bf16.try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window,
-                                     page_size, rope=rope)
+                                     page_size, rope=rope, **shaped)
         if out is not None:
             return out
     assert rope is None
     return paged_attention_simt(qkv, pages, block_table, ctx.seq_of_token, ctx.positions, nh, nkv,
-                                hd, scale, window, page_size)
+                                hd, scale, window, page_size, **shaped)
 
 
 # ----------------------------------------------------------------------------- sampling
@@ -417,3 +441,4 @@ def bmm_f32_out(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 from .linear import GatedLinear, Linear, add_to  # noqa: E402,F401
 from . import prenorm  # noqa: E402,F401
+from . import depth  # noqa: E402,F401

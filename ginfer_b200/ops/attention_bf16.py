@@ -218,12 +218,15 @@ def fuses_rope(qkv, ctx, hd: int, nh: int, nkv: int) -> bool:
     return qkv.dtype == torch.bfloat16 and ctx.decode_only and supports(hd, nh, nkv)
 
 
-def try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window, page_size, rope=None):
+def try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window, page_size, rope=None,
+            softcap: float = 0.0, slopes=None):
     """Run a bf16 kernel if one takes this head size; ``None`` hands the work to the plain
     fp32-arithmetic kernel.  ``rope``: see :func:`decode` (only where :func:`fuses_rope`).
     ``window``: the mask as ``ops.mask_span`` gives it (negative: chunks)."""
     if not supports(hd, nh, nkv):
         return None
+    if softcap or slopes is not None:
+        return None          # TODO shaped scores
     if ctx.decode_only:
         keys = min(abs(window), ctx.max_kv_len) if window else ctx.max_kv_len
         splits, parts = decode_partition(ctx.num_seqs, nh, nkv, keys)

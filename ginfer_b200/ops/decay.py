@@ -55,6 +55,20 @@ def gla_prepare(proj: torch.Tensor, z: torch.Tensor, HD: int, HV: int, q_scale: 
     return out
 
 
+def silu_f32(proj: torch.Tensor, width: int) -> torch.Tensor:
+    """``silu`` of the first ``width`` columns of ``proj [T, ...]`` as fp32 ``[T, width]``: the
+    operands of a linear attention whose q, k and v pass an activation and nothing else."""
+    _cuda(proj)
+    T = proj.shape[0]
+    assert proj.dim() == 2 and proj.stride(1) == 1 and width <= proj.shape[1]
+    out = torch.empty((T, width), dtype=torch.float32, device=proj.device)
+    f = _fn("decay_state", "gf_silu_f32",
+            [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p])
+    _ok(f(_p(proj), proj.stride(0), T, int(width), _p(out), _code(proj.dtype), _stream()),
+        "silu_f32")
+    return out
+
+
 # The recurrence keeps a column's rows of the state in registers: key sizes up to this.
 MAX_KEY_SIZE = 256
 
@@ -101,8 +115,10 @@ def recurrence(q, k, v, g, state: torch.Tensor, ctx, H: int, G: int, D: int, Vd:
 
 
 def gated_norm(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, group_size: int,
-               gate_first: bool, eps: float, dtype: torch.dtype) -> torch.Tensor:
-    """RMS norm of ``o [T, C]`` (fp32) in groups of ``group_size`` channels with a SiLU gate:
+               gate_first: bool, eps: float, dtype: torch.dtype, sigmoid_gate: bool = False
+               ) -> torch.Tensor:
+    """RMS norm of ``o [T, C]`` (fp32) in groups of ``group_size`` channels with a SiLU gate (a
+    plain sigmoid with ``sigmoid_gate``):
     ``gate_first``: ``y = o silu(gate)``, then ``y / rms(y) * w``; else ``o / rms(o) * w *
     silu(gate)``.  ``w`` has ``C`` weights, or ``group_size`` shared by the groups.  ``gate``:
     ``[T, C]``, fp32 or the activation dtype, rows may be strided.  Returns ``[T, C]`` in
@@ -117,7 +133,7 @@ def gated_norm(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, group_size:
             [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_int,
              c_int, c_int, c_int, c_void_p])
     shared = int(w.numel() == group_size and C != group_size)
-    _ok(f(_p(o), _p(gate), gate.stride(0), _code(gate.dtype), _p(w), shared, int(bool(gate_first)),
+    _ok(f(_p(o), _p(gate), gate.stride(0), _code(gate.dtype), _p(w), shared, int(bool(gate_first)) | (2 if sigmoid_gate else 0),
           float(eps), _p(out), T, C // group_size, int(group_size), _code(dtype), _stream()),
         "gated_norm")
     return out

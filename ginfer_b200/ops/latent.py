@@ -33,6 +33,30 @@ def prepare(qd: torch.Tensor, H: int, D: int, R: int, C: int, rot: int, freq: to
     return q_rot
 
 
+def norms(proj: torch.Tensor, q_col: int, Q: int, q_w, c_col: int, C: int, c_w, eps: float,
+          slot_mapping, c_pages):
+    """Out of a projection row ``proj [T, ...]``: the query latent (``Q`` channels from ``q_col``)
+    RMS-normed with ``q_w`` and returned ``[T, Q]`` in the row's dtype (``None`` for ``Q == 0``),
+    and the key/value latent (``C`` channels from ``c_col``) RMS-normed with ``c_w`` into the
+    token's slot of ``c_pages`` (skipped without ``slot_mapping``)."""
+    _cuda(proj, q_w, c_w, slot_mapping, c_pages)
+    T = proj.shape[0]
+    assert proj.dim() == 2 and proj.stride(1) == 1
+    assert q_col + Q <= proj.shape[1] and (slot_mapping is None or c_col + C <= proj.shape[1])
+    for w, n in ((q_w, Q), (c_w, C)):
+        assert w is None or (w.dtype == torch.float32 and w.numel() == n and w.is_contiguous())
+    if slot_mapping is not None:
+        assert c_pages.is_contiguous() and c_pages.dtype == proj.dtype and c_pages.shape[-1] == C
+    cq = torch.empty((T, Q), dtype=proj.dtype, device=proj.device) if Q else None
+    f = _fn("latent_attention", "gf_latent_norms",
+            [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_float,
+             c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _ok(f(_p(proj), proj.stride(0), int(q_col), int(Q), _p(q_w), _p(cq), int(c_col), int(C),
+          _p(c_w), float(eps), _p(slot_mapping), _p(c_pages), T, _code(proj.dtype), _stream()),
+        "latent_norms")
+    return cq
+
+
 KEY_TILE = 64           # keys a tile of the tensor-core kernel
 MAX_SPLITS = 8
 MIN_TILES_A_SPLIT = 4   # a share shorter than this costs more in the merge than it saves
@@ -56,9 +80,11 @@ def attention(q_lat: torch.Tensor, q_rot: torch.Tensor, c_pages: torch.Tensor,
     there) bounds the keys of a token and decides whether several blocks share them."""
     _cuda(q_lat, q_rot, c_pages, r_pages, block_table)
     H, T, C = q_lat.shape
-    R = q_rot.shape[2]
+    R = q_rot.shape[2] if q_rot is not None else 0       # no rotated part: both are None
     assert q_lat.dtype == torch.float32 and q_lat.is_contiguous()
-    assert q_rot.dtype == torch.float32 and q_rot.is_contiguous() and q_rot.shape[:2] == (T, H)
+    assert q_rot is None or (q_rot.dtype == torch.float32 and q_rot.is_contiguous()
+                             and q_rot.shape[:2] == (T, H))
+    assert (R == 0) == (r_pages is None)
     out = torch.empty((H, T, C), dtype=c_pages.dtype, device=q_lat.device)
     nsplit, part_o, part_ml = 1, None, None
     max_keys = int(getattr(ctx, "max_kv_len", 0) or 0)

@@ -69,12 +69,13 @@ def stream_update(x: torch.Tensor, act_dtype: torch.dtype, *, y=None, scale=None
 
 def qk_norm_rope(qkv: torch.Tensor, nh: int, nkv: int, hd: int, k_off: int, v_off: int, q_weight,
                  k_weight, eps: float, freqs, interleaved: bool, positions: torch.Tensor,
-                 slot_mapping, pages: torch.Tensor) -> None:
+                 slot_mapping, pages: torch.Tensor, q_temp=None) -> None:
     """Per head of ``qkv [T, ...]`` (q heads from column 0, k heads from ``k_off``): RMS norm with
     the weight of its kind (``None``: no norm), rotation of the first ``2 len(freqs)`` channels in
     pairs by ``position * freqs[i]`` (neighbours ``(2i, 2i+1)`` if ``interleaved``, else halves);
     q in place; with ``slot_mapping`` k goes to ``pages[0]`` and the values (columns from
-    ``v_off``, unchanged) to ``pages[1]``."""
+    ``v_off``, unchanged) to ``pages[1]``.  ``q_temp = (coef, every)``: the normed queries at
+    position ``p`` are multiplied by ``1 + coef * ln(floor((p + 1) / every) + 1)``."""
     _cuda(qkv, q_weight, k_weight, freqs, positions, slot_mapping, pages)
     assert qkv.dim() == 2 and qkv.stride(1) == 1
     assert pages.is_contiguous() and pages.dtype == qkv.dtype and pages.shape[0] == 2
@@ -86,9 +87,11 @@ def qk_norm_rope(qkv: torch.Tensor, nh: int, nkv: int, hd: int, k_off: int, v_of
         assert freqs.dtype == torch.float32 and freqs.is_contiguous()
     f = _fn("prenorm_stream", "gf_qk_norm_rope",
             [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+             c_float, c_int,
              c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    qt_coef, qt_every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
     _ok(f(_p(qkv), qkv.stride(0), qkv.shape[0], nh, nkv, hd, int(k_off), int(v_off), _p(q_weight),
-          _p(k_weight), float(eps), _p(freqs), n_pairs, int(bool(interleaved)), _p(positions),
+          _p(k_weight), float(eps), qt_coef, qt_every, _p(freqs), n_pairs, int(bool(interleaved)), _p(positions),
           _p(slot_mapping), _p(pages[0]), _p(pages[1]), _code(qkv.dtype), _stream()),
         "qk_norm_rope")
 

@@ -307,3 +307,106 @@ class PostNormBlock(Block):
 
 
 register_block("postnorm", PostNormBlock)
+
+
+class SandwichBlock(Block):
+    """Norms before AND behind every sublayer on a 32-bit stream: ``x <- x + norm1b(mixer(norm1(
+    x)))``, then ``x <- x + norm2b(ff(norm2(x)))``; a layer without a feed-forward is the first line
+    alone.  ``mixer_out_norm`` / ``feed_forward_out_norm`` are the norms behind the sublayers (the
+    layer's ``mixer_norm`` / ``feed_forward_norm`` the ones in front).
+
+    ``depth_states = n`` > 0: the layer ends with an average over the model's depth.  Its result
+    is kept as state ``n - 1`` of the step's history (``ctx.extras["depth_history"]``, made by the
+    embedding, whose output is state 0) and what goes on to the next layer is ``sum_j w[j] *
+    state_j`` over ``j < n`` with the layer's tensor ``depth_name`` (``n`` weights, 32-bit).
+
+    Every sublayer ends in ONE kernel: output norm, addition, (average,) and the norm in front of
+    the next sublayer, also the first norm of the NEXT run (``then``), which travels there in
+    ``ctx.extras["prenormed"]``."""
+
+    takes_next_norm = True
+
+    def __init__(self, layer_spec, mixer_out_norm, feed_forward_out_norm=None,
+                 depth_states: int = 0, depth_name: str = "dwa"):
+        self.spec = layer_spec
+        self.mixer_norm = make_part("norm", layer_spec.mixer_norm)
+        self.mixer = make_part("mixer", layer_spec.mixer)
+        self.mixer_out_norm = make_part("norm", mixer_out_norm)
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_out_norm = None
+        if layer_spec.feed_forward is not None:
+            self.feed_forward_norm = make_part("norm", layer_spec.feed_forward_norm)
+            self.feed_forward = make_part("feed_forward", layer_spec.feed_forward)
+            self.feed_forward_out_norm = make_part("norm", feed_forward_out_norm)
+        for n in (self.mixer_norm, self.mixer_out_norm, self.feed_forward_norm,
+                  self.feed_forward_out_norm):
+            if n is not None and not hasattr(n, "weight32"):
+                raise ValueError("the norms of this block are RMS norms (kind 'rmsnorm')")
+        self.depth_states, self.depth_name = int(depth_states), depth_name
+        if self.depth_states == 1 or self.depth_states < 0:
+            raise ValueError("an average over the depth takes at least two states")
+        self.depth_w = None
+
+    def parts(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.mixer_out_norm,
+                                 self.feed_forward_norm, self.feed_forward,
+                                 self.feed_forward_out_norm) if p is not None)
+
+    def tensor_specs(self):
+        from .base import TensorSpec
+        out = []
+        for p in self.parts():
+            out.extend(p.tensor_specs())
+        if self.depth_states:
+            out.append(TensorSpec(self.depth_name, (self.depth_states,), "f32"))
+        return out
+
+    def first_norm(self):
+        return self.mixer_norm
+
+    def load(self, tensors, dtype, device):
+        for p in self.parts():
+            p.load(tensors, dtype, device)
+        if self.depth_states:
+            self.depth_w = tensors[self.depth_name].float().contiguous()
+
+    def _end(self, x, y, out_norm, ctx, nxt, average=False):
+        """One sublayer's end -> ``(stream, norm of the stream for ``nxt`` or None)``."""
+        from ..ops import depth
+        kw = {}
+        if average and self.depth_states:
+            hist = ctx.extras.get("depth_history")
+            if hist is None or hist.shape[0] < self.depth_states:
+                raise RuntimeError("this layer averages over the depth, but the step has no "
+                                   "history of that many states (the embedding makes it)")
+            kw.update(history=hist, mix_weights=self.depth_w, n_before=self.depth_states - 1)
+        fused = nxt is not None and hasattr(nxt, "weight32") and not nxt.weight_offset
+        if fused:
+            kw.update(next_weight=nxt.weight32(), next_eps=nxt.eps)
+        x, n = depth.sandwich_update(x, y, out_norm.weight32(), out_norm.eps, ctx.dtype, **kw)
+        if nxt is not None and not fused:
+            n = nxt.forward(x, None, want_sum=False, out_dtype=ctx.dtype)[1]
+        return x, n
+
+    def forward(self, x, delta, ctx, cache, then=None):
+        if delta is not None:
+            x = x.float() + delta.float()
+        elif x.dtype != torch.float32:
+            x = x.float()
+        kept = ctx.extras.pop("prenormed", None)
+        if kept is not None and kept[0] is x and kept[1] is self.mixer_norm:
+            n = kept[2]
+        else:
+            n = self.mixer_norm.forward(x, None, want_sum=False, out_dtype=ctx.dtype)[1]
+        a = self.mixer.forward(n, ctx, cache)
+        if self.feed_forward is not None:
+            x, n2 = self._end(x, a, self.mixer_out_norm, ctx, self.feed_forward_norm)
+            f = self.feed_forward.forward(n2, ctx)
+            x, n_next = self._end(x, f, self.feed_forward_out_norm, ctx, then, average=True)
+        else:
+            x, n_next = self._end(x, a, self.mixer_out_norm, ctx, then, average=True)
+        if n_next is not None:
+            ctx.extras["prenormed"] = (x, then, n_next)
+        return x, None
+
+
+register_block("sandwich", SandwichBlock)

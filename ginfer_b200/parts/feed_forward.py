@@ -80,3 +80,38 @@ class ClampedGLU(FeedForward):
 
 
 register_feed_forward("clamped_glu", ClampedGLU)
+
+
+class DenseActivationMLP(FeedForward):
+    """Two matrices with an activation between them: ``W_down act(W_up x + b_up) + b_down`` with
+    ``act = relu^2`` (the only one so far); biases optional.  The output leaves in fp32 for the
+    norm that follows it."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "relu2",
+                 bias: bool = True, prefix: str = "mlp", up_name: str = "up",
+                 down_name: str = "down"):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        if activation != "relu2":
+            raise ValueError(f"activation {activation!r}: only 'relu2' is there")
+        self.activation, self.bias = activation, bool(bias)
+        p = prefix + "." if prefix else ""
+        self.up_key, self.down_key = p + up_name, p + down_name
+
+    def tensor_specs(self):
+        h, i = self.hidden_size, self.intermediate_size
+        out = [TensorSpec(self.up_key, (i, h)), TensorSpec(self.down_key, (h, i))]
+        if self.bias:
+            out += [TensorSpec(self.up_key + ".b", (i,), "bias"),
+                    TensorSpec(self.down_key + ".b", (h,), "bias")]
+        return out
+
+    def load(self, tensors, dtype, device):
+        b = (lambda k: tensors[k + ".b"].float().contiguous()) if self.bias else (lambda k: None)
+        self.up = ops.Linear(tensors[self.up_key], b(self.up_key))
+        self.down = ops.Linear(tensors[self.down_key], b(self.down_key), out_dtype=torch.float32)
+
+    def forward(self, x, ctx):
+        return self.down(ops.activation_(self.up(x), self.activation))
+
+
+register_feed_forward("dense_mlp", DenseActivationMLP)

@@ -8,6 +8,12 @@ one weight vector for all heads (``q.norm``, ``k.norm``), then rotated by the po
 ``n / (heads / kv_heads)``.  Head ``n``'s output is multiplied by ``sigmoid(W_g h)_n`` before
 ``W_o``.
 
+Options for designs without rotation: ``position = None`` (positions enter only through what
+follows); ``q_temp = (coef, every)``: the normed query at position ``p`` is multiplied by ``1 + coef
+* ln(floor((p + 1) / every) + 1)``; ``softcap``: ``score <- cap * tanh(score / cap)`` after the
+scale; ``distance_slope_base = b``: head ``n`` of ``H`` takes ``2^(-b (n + 1) / H) * (p - j)`` off the
+score of key ``j`` (after the cap, before the softmax).
+
 One product over the joined matrices gives q, k, (v) and the gates; one kernel norms and rotates q
 in place and writes the normed, rotated k and the values to their cache slots; the attention
 kernels of the plain grouped-query mixer run over that cache; one kernel applies the gates.
@@ -25,9 +31,10 @@ from .plan import PartSpec
 
 class NormedGatedAttention(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
-                 scale: float, position: PartSpec, window: int = 0, qk_norm: bool = True,
+                 scale: float, position: PartSpec | None, window: int = 0, qk_norm: bool = True,
                  qk_norm_eps: float = 1e-6, value_projection: bool = False,
-                 head_gate: bool = True, prefix: str = "mix"):
+                 head_gate: bool = True, prefix: str = "mix", q_temp=None,
+                 softcap: float | None = None, distance_slope_base: float | None = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads are not a multiple of {num_kv_heads} kv heads")
         self.hidden_size = int(hidden_size)
@@ -36,12 +43,25 @@ class NormedGatedAttention(Mixer):
         self.qk_norm, self.eps = bool(qk_norm), float(qk_norm_eps)
         self.value_projection, self.gated = bool(value_projection), bool(head_gate)
         self.prefix = prefix + "." if prefix else ""
-        self.position = make_part("position", position)
-        if not hasattr(self.position, "frequencies"):
-            raise ValueError("this mixer rotates channel pairs by frequencies; its position "
-                             "encoding must give them (kind 'pair_rotary')")
-        if self.position.dims > self.hd:
-            raise ValueError(f"{self.position.dims} rotated channels do not fit a head of {self.hd}")
+        self.position = make_part("position", position) if position is not None else None
+        if self.position is not None:
+            if not hasattr(self.position, "frequencies"):
+                raise ValueError("this mixer rotates channel pairs by frequencies; its position "
+                                 "encoding must give them (kind 'pair_rotary')")
+            if self.position.dims > self.hd:
+                raise ValueError(f"{self.position.dims} rotated channels do not fit a head of "
+                                 f"{self.hd}")
+        self.q_temp = None
+        if q_temp is not None:
+            coef, every = float(q_temp[0]), int(q_temp[1])
+            if every <= 0:
+                raise ValueError(f"q_temp: 'every' must be positive, got {every}")
+            self.q_temp = (coef, every)
+        self.softcap = float(softcap) if softcap else 0.0
+        if self.softcap < 0:
+            raise ValueError(f"softcap must be positive, got {softcap}")
+        self.slope_base = None if distance_slope_base is None else float(distance_slope_base)
+        self.slopes = None
 
     def _n(self, name):
         return self.prefix + name
@@ -57,7 +77,7 @@ class NormedGatedAttention(Mixer):
         if self.gated:
             out.append(TensorSpec(self._n("g"), (nh, W)))
         out.append(TensorSpec(self._n("o"), (W, nh * hd)))
-        return out + self.position.tensor_specs()
+        return out + (self.position.tensor_specs() if self.position is not None else [])
 
     def load(self, tensors, dtype, device):
         nh, nkv, hd = self.nh, self.nkv, self.hd
@@ -79,7 +99,11 @@ class NormedGatedAttention(Mixer):
         self.q_w = tensors[self._n("q.norm")].float().contiguous() if self.qk_norm else None
         self.k_w = tensors[self._n("k.norm")].float().contiguous() if self.qk_norm else None
         self.out = ops.Linear(tensors[self._n("o")], None, out_dtype=torch.float32)
-        self.position.load(tensors, dtype, device)
+        if self.position is not None:
+            self.position.load(tensors, dtype, device)
+        if self.slope_base is not None:
+            self.slopes = torch.tensor([2.0 ** (-self.slope_base * (n + 1) / nh)
+                                        for n in range(nh)], dtype=torch.float32, device=device)
 
     def cache_spec(self):
         return PagedKVSpec(self.nkv, self.hd, self.window)
@@ -87,12 +111,15 @@ class NormedGatedAttention(Mixer):
     def forward(self, x, ctx, cache):
         nh, nkv, hd = self.nh, self.nkv, self.hd
         qkv = self.qkv(x)
+        pos = self.position
         prenorm.qk_norm_rope(qkv, nh, nkv, hd, self.k_off, self.v_off, self.q_w, self.k_w,
-                             self.eps, self.position.frequencies(), self.position.interleaved,
+                             self.eps, pos.frequencies() if pos is not None else None,
+                             pos.interleaved if pos is not None else False,
                              ctx.positions, cache.slot_mapping if cache.write else None,
-                             cache.pages)
+                             cache.pages, q_temp=self.q_temp)
         o = ops.paged_attention(qkv, cache.pages, cache.block_table, ctx, nh, nkv, hd, self.scale,
-                                cache.window, cache.page_size)
+                                cache.window, cache.page_size, softcap=self.softcap,
+                                slopes=self.slopes)
         if self.gated:
             prenorm.head_gate(o, qkv[:, self.g_off:self.g_off + nh], nh, hd)
         return self.out(o)

@@ -37,6 +37,13 @@ class RMSNorm(Norm):
         if self.weight_offset:
             self.weight = (self.weight.float() + self.weight_offset).contiguous()
 
+    def weight32(self) -> torch.Tensor:
+        """The weight in 32-bit (made once), for kernels that apply this norm inside a pass of
+        their own."""
+        if self._w32 is None:
+            self._w32 = self.weight.float().contiguous()
+        return self._w32
+
     def add_output(self, x, y, act_dtype, want_act=True):
         """For blocks whose norms sit on the sublayers' outputs: ``x' = x + norm(y)`` on the fp32
         stream ``x``; returns ``(x', x' in act_dtype or None)``."""
