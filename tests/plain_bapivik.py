@@ -27,10 +27,11 @@ def silu(z):
 
 
 # ----------------------------------------------------------------------------- embedding
-def embed(tokens, P):
+def embed(tokens, P, positions=True):
     """Token row plus the learned row of the token's position, unscaled."""
     T = len(tokens)
-    return P["embed"][torch.tensor(tokens)] + P["pos"][:T]
+    x = P["embed"][torch.tensor(tokens)]
+    return x + P["pos"][:T] if positions else x
 
 
 # ----------------------------------------------------------------------------- lightning
@@ -60,7 +61,7 @@ def latent_of(h, P, pre, eps, rnd=same):
     return rnd(rms_norm(rnd(h @ P[pre + "dkv"].T), P[pre + "dkv.norm"], eps))
 
 
-def latent_attention(h, c, P, pre, m, eps, rnd=same):
+def latent_attention(h, c, P, pre, m, eps, rnd=same, gated=True):
     """``c``: the latent vectors the layer reads (its own, or another layer's)."""
     H, D, Vd = m["heads"], m["dim"], m["vdim"]
     T = h.shape[0]
@@ -75,7 +76,7 @@ def latent_attention(h, c, P, pre, m, eps, rnd=same):
         i = torch.arange(T)
         s = s.masked_fill(i[None, :] > i[:, None], -math.inf)
         out[:, n] = torch.softmax(s, dim=-1) @ v[:, n]
-    out = rnd(out * gate[:, :, None])
+    out = rnd(out * gate[:, :, None]) if gated else rnd(out)
     return out.reshape(T, H * Vd) @ P[pre + "o"].T
 
 
@@ -95,7 +96,7 @@ def visible(T, window):
     return ok
 
 
-def attention(h, P, pre, m, eps, rnd=same):
+def attention(h, P, pre, m, eps, rnd=same, without=()):
     H, G, D = m["heads"], m["kv_heads"], m["dim"]
     T = h.shape[0]
     q = rnd(h @ P[pre + "q"].T).reshape(T, H, D)
@@ -104,19 +105,20 @@ def attention(h, P, pre, m, eps, rnd=same):
     q = rms_norm(q, P[pre + "q.norm"], eps)
     kn = rnd(rms_norm(k, P[pre + "k.norm"], eps))
     qt = m.get("q_temp")
-    if qt:
+    if qt and "q_temp" not in without:
         q = q * query_temperature(T, qt["coef"], qt["every"])[:, None, None]
     q = rnd(q)
-    ok = visible(T, (m.get("mask") or {}).get("size", 0))
+    ok = visible(T, 0 if "window" in without else (m.get("mask") or {}).get("size", 0))
     dist = (torch.arange(T)[:, None] - torch.arange(T)[None, :]).to(F64)
-    cap = m.get("softcap")
+    cap = None if "softcap" in without else m.get("softcap")
     out = torch.zeros(T, H, D, dtype=F64)
     for n in range(H):
         g = n // (H // G)
         s = (q[:, n] @ kn[:, g].T) * m["scale"]
         if cap:
             s = cap * torch.tanh(s / cap)
-        s = s - 2.0 ** (-8.0 * (n + 1) / H) * dist
+        if "slopes" not in without:
+            s = s - 2.0 ** (-8.0 * (n + 1) / H) * dist
         s = s.masked_fill(~ok, -math.inf)
         out[:, n] = torch.softmax(s, dim=-1) @ v[:, g]
     return rnd(out.reshape(T, H * D)) @ P[pre + "o"].T
@@ -129,11 +131,16 @@ def dense(h, P, pre, rnd=same):
 
 
 # ----------------------------------------------------------------------------- the model
-def forward(cfg, P, tokens, rnd=same, layers_out=None):
+def forward(cfg, P, tokens, rnd=same, layers_out=None, without=()):
     """Logits ``[T, vocab]`` of one sequence.  ``layers_out``: a list that receives the stream
-    after every layer (after the depth average)."""
+    after every layer (after the depth average).  ``without``: mechanisms to leave out (``pos``,
+    ``dwa``, ``norm_b``, ``gate``, ``shared``, ``q_temp``, ``softcap``, ``slopes``, ``window``,
+    ``logit_cap``), so that a test can show that each one moves the logits."""
     eps = cfg["norm"]["eps"]
-    x = embed(tokens, P)
+    x = embed(tokens, P, "pos" not in without)
+
+    def out_norm(y, name):
+        return y if "norm_b" in without else rms_norm(y, P[name], eps)
     X = [x]                                      # the embedding output and every layer's result
     latents = {}
     for i, L in enumerate(cfg["layers"]):
@@ -143,26 +150,30 @@ def forward(cfg, P, tokens, rnd=same, layers_out=None):
             a = lightning(h, P, pre + "mix.", m, eps, rnd)
         elif L["type"] == "latent_attention":
             src = m.get("kv_from")
+            if src is not None and "shared" in without:      # as if it read the layer before it
+                src = max(k for k in latents if k < i)
             if src is None:
                 latents[i] = latent_of(h, P, pre + "mix.", eps, rnd)
                 src = i
-            a = latent_attention(h, latents[src], P, pre + "mix.", m, eps, rnd)
+            a = latent_attention(h, latents[src], P, pre + "mix.", m, eps, rnd,
+                                 gated="gate" not in without)
         elif L["type"] == "attention":
-            a = attention(h, P, pre + "mix.", m, eps, rnd)
+            a = attention(h, P, pre + "mix.", m, eps, rnd, without)
         else:
             raise ValueError(L["type"])
-        x = x + rms_norm(a, P[pre + "norm1b"], eps)
+        x = x + out_norm(a, pre + "norm1b")
         if L.get("mlp") is not None:
             h = rnd(rms_norm(x, P[pre + "norm2"], eps))
-            x = x + rms_norm(dense(h, P, pre + "mlp.", rnd), P[pre + "norm2b"], eps)
+            x = x + out_norm(dense(h, P, pre + "mlp.", rnd), pre + "norm2b")
         X.append(x)
         w = P[pre + "dwa"]
-        x = sum(w[j] * X[j] for j in range(i + 2))
+        if "dwa" not in without:
+            x = sum(w[j] * X[j] for j in range(i + 2))
         if layers_out is not None:
             layers_out.append(x)
     y = rnd(rms_norm(x, P["final.norm"], eps))
     logits = y @ P["embed"].T
     cap = cfg.get("logit_softcap")
-    if cap:
+    if cap and "logit_cap" not in without:
         logits = cap * torch.tanh(logits / cap)
     return logits
