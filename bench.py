@@ -27,6 +27,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -260,11 +261,11 @@ def prefill_timed(eng, tokens: int, reps: int, warmup: int, seed: int):
 
 
 # ----------------------------------------------------------------------------- another design
-# ``--design vilepel|zolapel|pimidra``: prefill and decode throughput of another design at layer sizes that
+# ``--design vilepel|zolapel|pimidra|bapivik``: prefill and decode throughput of another design at layer sizes that
 # resemble a real model's (random weights), beside Qwen2 at equal width, heads, feed-forward size
 # and layer count.  The default workload and its JSON line are untouched by this option.
 def vilepel_config(width, heads, dim, rot, vdim, rank, window, ff, experts, top, expert_ff,
-                   layers, vocab=32768):
+                   layers, vocab=32768, routed=True):
     def latent():
         return {"type": "latent_attention", "mixer": {
             "heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": rank,
@@ -279,6 +280,8 @@ def vilepel_config(width, heads, dim, rot, vdim, rank, window, ff, experts, top,
     moe = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0},
            "router": {"experts": experts, "top": top}}
     kinds = [(latent, dense), (delta, moe), (latent, moe), (delta, dense)]
+    if not routed:
+        kinds = [(latent, dense), (delta, dense)] * 2
     return {"architecture": "Vilepel", "width": width, "vocab": vocab, "norm": {"eps": 1e-5},
             "embedding": {"scale": 1.0}, "torch_dtype": "bfloat16",
             "layers": [dict(kinds[i % 4][0](), mlp=kinds[i % 4][1]) for i in range(layers)]}
@@ -324,6 +327,46 @@ def pimidra_config(width, heads, kv_heads, dim, chunk, ff, experts, top, expert_
             "layers": [dict(kinds[i % 4][0](), mlp=kinds[i % 4][1]) for i in range(layers)]}
 
 
+def bapivik_config(width, heads, kv_heads, dim, rank, q_rank, window, ff, layers, vocab=32768,
+                   max_positions=8192):
+    """Layers in turns of four, each with a dense relu^2 feed-forward: latent attention, latent
+    attention over the first one's latent vectors, windowed attention with shaped scores, linear
+    attention with fixed decays."""
+    def latent(source):
+        m = {"heads": heads, "dim": dim, "vdim": dim, "kv_rank": rank, "q_rank": q_rank,
+             "scale": dim ** -0.5}
+        if source is not None:
+            m["kv_from"] = source
+        return {"type": "latent_attention", "mixer": m}
+
+    def attention():
+        return {"type": "attention", "mixer": {
+            "heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+            "mask": {"size": window}, "softcap": 30.0, "q_temp": {"coef": 0.25, "every": 256}}}
+
+    def lightning():
+        return {"type": "lightning", "mixer": {
+            "heads": heads, "dim": dim, "vdim": dim,
+            "decay": [math.exp(-2.0 ** (-3.0 - 5.0 * n / heads)) for n in range(heads)]}}
+    out = []
+    for i in range(layers):
+        turn = i % 4
+        mixer = (latent(None) if turn == 0 else latent(i - 1) if turn == 1 else
+                 attention() if turn == 2 else lightning())
+        out.append(dict(mixer, mlp={"kind": "dense", "ff": ff}))
+    return {"architecture": "Bapivik", "width": width, "vocab": vocab, "norm": {"eps": 1e-5},
+            "max_positions": max_positions, "logit_softcap": 30.0, "torch_dtype": "bfloat16",
+            "layers": out}
+
+
+BAPIVIK_SIZES = {
+    # width, heads, kv heads, dim, latent rank, query rank, window, two-matrix ff (Vilepel beside
+    # it: a three-matrix ff of two thirds of that)
+    "s": (1024, 8, 2, 64, 256, 384, 512, 4224),
+    "m": (2048, 16, 4, 128, 512, 768, 1024, 8448),
+}
+
+
 PIMIDRA_SIZES = {
     # width, heads, kv heads, dim, chunk, dense ff, experts, top, expert ff, state-space heads,
     # their value size, state size
@@ -363,6 +406,16 @@ def design_configs(design: str, name: str, layers: int) -> dict:
                           intermediate_size=2 * top * eff // 3, vocab_size=32768,
                           use_sliding_window=True, sliding_window=window, max_window_layers=0),
         }
+    if design == "bapivik":
+        # beside it the closest design the engine has, Vilepel (latent attention and a recurrent
+        # mixer in turns, an fp32 stream), with dense feed-forwards only, at the same width, heads,
+        # head size, latent size, window, feed-forward arithmetic and layer count
+        width, heads, kv, dim, rank, q_rank, window, ff = BAPIVIK_SIZES[name]
+        return {
+            "bapivik": bapivik_config(width, heads, kv, dim, rank, q_rank, window, ff, layers),
+            "vilepel": vilepel_config(width, heads, dim, dim // 2, dim, rank, window, 2 * ff // 3,
+                                      1, 1, 1, layers, routed=False),
+        }
     if design == "pimidra":
         # beside it the closest design the engine has, Vilepel (attention with a bounded reach and a
         # recurrent mixer in turns, dense and routed feed-forwards, an fp32 stream), at the same
@@ -391,11 +444,12 @@ def run_design(args) -> int:
     from ginfer_b200.engine.llm import Engine
     out = {"design": args.design,
            "beside": ("vilepel at equal width, heads, head size, feed-forward sizes, reach and "
-                      "layers" if args.design == "pimidra" else
+                      "layers" if args.design in ("pimidra", "bapivik") else
                       "qwen2 at equal width, heads, feed-forward arithmetic and layer runs"),
            "dtype": "bfloat16", "data": "synthetic", "sizes": {}}
     layers = args.layers or 8
-    sizes = {"zolapel": ZOLAPEL_SIZES, "pimidra": PIMIDRA_SIZES}.get(args.design, DESIGN_SIZES)
+    sizes = {"zolapel": ZOLAPEL_SIZES, "pimidra": PIMIDRA_SIZES,
+             "bapivik": BAPIVIK_SIZES}.get(args.design, DESIGN_SIZES)
     for name in (args.size.split(",") if args.size else sorted(sizes)):
         cfgs = design_configs(args.design, name, layers)
         width = sizes[name][0]
@@ -727,7 +781,7 @@ def main() -> int:
                     help="tokens a step of the long prompt in --scenario longctx (default 2,048)")
     ap.add_argument("--scenario", choices=SCENARIOS, default=None,
                     help="run a serving workload through the entry point instead of the benchmark")
-    ap.add_argument("--design", choices=["vilepel", "zolapel", "pimidra"], default=None,
+    ap.add_argument("--design", choices=["vilepel", "zolapel", "pimidra", "bapivik"], default=None,
                     help="measure another design beside Qwen2 at equal size instead of the benchmark")
     ap.add_argument("--size", default=None, help="with --design: sizes to run, e.g. s,m")
     args = ap.parse_args()

@@ -124,7 +124,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
                    const int* __restrict__ positions, bf16* __restrict__ out,
                    float* __restrict__ po, float* __restrict__ pml, int nh, int nkv,
                    int page_size, int window, float scale_log2, int splits, int fused_merge,
-                   int tbl_off, int tbl_cap, const RopeArgs rope) {
+                   int tbl_off, int tbl_cap, const RopeArgs rope, const ScoreShape shape) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ bool last_split;
   bf16* ks = reinterpret_cast<bf16*>(smem_raw);                 // [STAGES][KT][ROW]
@@ -159,6 +159,10 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
   for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   const int lo2[2] = {begin, begin}, hi2[2] = {end - 1, end - 1};
+  // shaped scores: the rows are heads, all at position p
+  const bool is_shaped = shaped(shape);
+  const RowShape rs = row_shape(shape, scale_log2, g < nrows ? h0 + g : -1,
+                                g + 8 < nrows ? h0 + g + 8 : -1, p, p);
 
   const int ntiles = begin < end ? (end - begin + KT - 1) / KT : 0;
   // this split's block-table entries -> shared memory
@@ -273,7 +277,9 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
     if (col0 < end) {
       float s[2][4] = {};
       qk_tile<2>(s, qf, ks + st * KT * ROW, warp * 16, lane);
-      if (col0 + 16 <= end)
+      if (is_shaped)
+        softmax_update<2, true, true>(s, o, m, l, col0, lo2, hi2, scale_log2, lane, &rs);
+      else if (col0 + 16 <= end)
         softmax_update<2, false>(s, o, m, l, col0, lo2, hi2, scale_log2, lane);
       else
         softmax_update<2, true>(s, o, m, l, col0, lo2, hi2, scale_log2, lane);
@@ -851,7 +857,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
                     const bf16* __restrict__ vpages, const int* __restrict__ block_table,
                     int table_stride, const int* __restrict__ cu_seqlens_q,
                     const int* __restrict__ kv_lens, bf16* __restrict__ out, int nh, int nkv,
-                    int page_size, int window, float scale_log2, int tbl_off, int tbl_cap) {
+                    int page_size, int window, float scale_log2, int tbl_off, int tbl_cap,
+                    const ScoreShape shape) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);                 // [QT][ROW]
   bf16* ks = qs + QT * ROW;                                     // [STAGES][KT][ROW]
@@ -906,6 +913,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
   float o[MT][HD / 8][4];
   float m[MT][2], l[MT][2];
   int lo2[MT][2], hi2[MT][2];                  // visibility bounds of this thread's rows
+  const bool is_shaped = shaped(shape);
+  RowShape rs[MT];                             // shaped scores: the rows are positions of one head
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
@@ -919,6 +928,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
       hi2[mt][i] = r < rows ? p : -1;          // rows past the end see nothing
       lo2[mt][i] = first_visible_key(p, window);
     }
+    const int p0 = pos0 + r0 + warp * WROWS + mt * 16 + g;
+    rs[mt] = row_shape(shape, scale_log2, head, head, p0, p0 + 8);
   }
   const int warp_hi = min(p_last, pos0 + r0 + warp * WROWS + WROWS - 1);
   const int warp_lo = first_visible_key(pos0 + r0 + warp * WROWS, window);
@@ -967,7 +978,13 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
                           col0 >= first_visible_key(first_p + WROWS - 1, window);
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
-      if (interior)
+      if (is_shaped && interior)
+        softmax_update<8, false, true>(s[mt], o[mt], m[mt], l[mt], col0, lo2[mt], hi2[mt],
+                                       scale_log2, lane, &rs[mt]);
+      else if (is_shaped)
+        softmax_update<8, true, true>(s[mt], o[mt], m[mt], l[mt], col0, lo2[mt], hi2[mt],
+                                      scale_log2, lane, &rs[mt]);
+      else if (interior)
         softmax_update<8, false>(s[mt], o[mt], m[mt], l[mt], col0, lo2[mt], hi2[mt], scale_log2,
                                  lane);
       else
@@ -1040,7 +1057,8 @@ static int attn_decode_impl(const void* q, int q_row_stride, const void* kpages,
                             const void* vpages, const int* block_table, int table_stride,
                             const int* cu_seqlens_q, const int* positions, void* out,
                             void* scratch, int B, int nh, int nkv, int page_size, int window,
-                            float scale, int splits, const RopeArgs& rope, void* stream) {
+                            float scale, int splits, const RopeArgs& rope, void* stream,
+                            const ScoreShape shape = ScoreShape{0.f, nullptr}) {
   if (B <= 0) return 0;
   if (nkv <= 0 || nh <= 0 || nh % nkv || splits < 1) return -3;
   auto st = (cudaStream_t)stream;
@@ -1086,13 +1104,14 @@ static int attn_decode_impl(const void* q, int q_row_stride, const void* kpages,
                                       (const bf16*)vpages, block_table, table_stride,
                                       cu_seqlens_q, positions, (bf16*)out, (float*)nullptr,
                                       (float*)nullptr, nh, nkv, page_size, window, scale * LOG2E,
-                                      splits, 2, (int)work, tbl_cap, rope);
+                                      splits, 2, (int)work, tbl_cap, rope, shape);
   }
   const int fused = (size_t)B * nkv * chunks <= (size_t)kMaxDecodeGroups ? 1 : 0;
   int rc = launch_kernel(attn_decode_kernel, grid, dim3(NTHREADS), smem, st, (const bf16*)q,
                          q_row_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
                          table_stride, cu_seqlens_q, positions, (bf16*)out, po, pml, nh, nkv,
-                         page_size, window, scale * LOG2E, splits, fused, (int)work, tbl_cap, rope);
+                         page_size, window, scale * LOG2E, splits, fused, (int)work, tbl_cap, rope,
+                         shape);
   if (rc || splits == 1 || fused) return rc;
   return launch_kernel(attn_decode_merge_kernel, dim3(nh, B), dim3(HD), 0, st, (const float*)po,
                        (const float*)pml, cu_seqlens_q, (bf16*)out, nh, splits);
@@ -1192,11 +1211,26 @@ GF_EXPORT int gf_attn_decode_rope(const void* q, int q_row_stride, void* kpages,
                           scale, splits, RopeArgs{rope_table, rot, 1, write_kv ? 1 : 0}, stream);
 }
 
-GF_EXPORT int gf_attn_prefill(const void* q, int q_row_stride, const void* kpages,
-                              const void* vpages, const int* block_table, int table_stride,
-                              const int* cu_seqlens_q, const int* kv_lens, void* out, int B,
-                              int max_q_len, int nh, int nkv, int page_size, int window,
-                              float scale, void* stream) {
+// gf_attn_decode with shaped scores: `softcap` > 0 caps them (cap * tanh(score / cap)), `slopes`
+// (fp32 [nh] or null) takes slope * (p - c) off the score of the key at c.
+GF_EXPORT int gf_attn_decode_shaped(const void* q, int q_row_stride, const void* kpages,
+                                    const void* vpages, const int* block_table, int table_stride,
+                                    const int* cu_seqlens_q, const int* positions, void* out,
+                                    void* scratch, int B, int nh, int nkv, int page_size,
+                                    int window, float scale, int splits, float softcap,
+                                    const float* slopes, void* stream) {
+  if (softcap < 0.f) return -3;
+  return attn_decode_impl(q, q_row_stride, kpages, vpages, block_table, table_stride,
+                          cu_seqlens_q, positions, out, scratch, B, nh, nkv, page_size, window,
+                          scale, splits, RopeArgs{nullptr, 0, 0, 0}, stream,
+                          ScoreShape{softcap, slopes});
+}
+
+static int attn_prefill_impl(const void* q, int q_row_stride, const void* kpages,
+                             const void* vpages, const int* block_table, int table_stride,
+                             const int* cu_seqlens_q, const int* kv_lens, void* out, int B,
+                             int max_q_len, int nh, int nkv, int page_size, int window,
+                             float scale, void* stream, const ScoreShape shape) {
   if (B <= 0 || max_q_len <= 0) return 0;
   if (nh % nkv) return -3;
   auto st = (cudaStream_t)stream;
@@ -1214,7 +1248,30 @@ GF_EXPORT int gf_attn_prefill(const void* q, int q_row_stride, const void* kpage
   return launch_kernel(attn_prefill_kernel, grid, dim3(NTHREADS), smem, st, (const bf16*)q,
                        q_row_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
                        table_stride, cu_seqlens_q, kv_lens, (bf16*)out, nh, nkv, page_size, window,
-                       scale * LOG2E, (int)work, tbl_cap);
+                       scale * LOG2E, (int)work, tbl_cap, shape);
+}
+
+GF_EXPORT int gf_attn_prefill(const void* q, int q_row_stride, const void* kpages,
+                              const void* vpages, const int* block_table, int table_stride,
+                              const int* cu_seqlens_q, const int* kv_lens, void* out, int B,
+                              int max_q_len, int nh, int nkv, int page_size, int window,
+                              float scale, void* stream) {
+  return attn_prefill_impl(q, q_row_stride, kpages, vpages, block_table, table_stride,
+                           cu_seqlens_q, kv_lens, out, B, max_q_len, nh, nkv, page_size, window,
+                           scale, stream, ScoreShape{0.f, nullptr});
+}
+
+// The same with shaped scores (see gf_attn_decode_shaped).
+GF_EXPORT int gf_attn_prefill_shaped(const void* q, int q_row_stride, const void* kpages,
+                                     const void* vpages, const int* block_table, int table_stride,
+                                     const int* cu_seqlens_q, const int* kv_lens, void* out,
+                                     int B, int max_q_len, int nh, int nkv, int page_size,
+                                     int window, float scale, float softcap, const float* slopes,
+                                     void* stream) {
+  if (softcap < 0.f) return -3;
+  return attn_prefill_impl(q, q_row_stride, kpages, vpages, block_table, table_stride,
+                           cu_seqlens_q, kv_lens, out, B, max_q_len, nh, nkv, page_size, window,
+                           scale, stream, ScoreShape{softcap, slopes});
 }
 
 // ----------------------------------------------------------------------------- no allocation

@@ -161,12 +161,43 @@ __device__ __forceinline__ float fast_exp2(float x) {   // 2^x; -inf -> 0
   return y;
 }
 
+// Shaped scores.  With a cap, score <- cap * tanh(score / cap) after the scale; with slopes (one a
+// head), slope * (p - c) is then taken off the score of the key at c for the query at p.
+struct ScoreShape {
+  float cap;              // 0: no cap
+  const float* slopes;    // [heads], or null: no distance bias
+};
+__device__ __forceinline__ bool shaped(const ScoreShape& sh) {
+  return sh.cap > 0.f || sh.slopes != nullptr;
+}
+// What a thread needs of the shape for its two rows, in log2 units.
+struct RowShape {
+  float k2;               // 2 log2(e) scale / cap: exp(2 x / cap) = 2^(k2 dot)
+  float cap_l2;           // cap log2(e); 0: no cap
+  float slope[2];         // slope log2(e) of the two rows' heads
+  int qpos[2];            // the two rows' positions
+};
+__device__ __forceinline__ RowShape row_shape(const ScoreShape& sh, float scale_log2, int h0,
+                                              int h1, int p0, int p1) {
+  RowShape r;
+  r.cap_l2 = sh.cap > 0.f ? sh.cap * 1.4426950408889634f : 0.f;
+  r.k2 = sh.cap > 0.f ? 2.f * scale_log2 / sh.cap : 0.f;
+  r.slope[0] = sh.slopes && h0 >= 0 ? sh.slopes[h0] * 1.4426950408889634f : 0.f;
+  r.slope[1] = sh.slopes && h1 >= 0 ? sh.slopes[h1] * 1.4426950408889634f : 0.f;
+  r.qpos[0] = p0;
+  r.qpos[1] = p1;
+  return r;
+}
+
 // MASKED = false: every column is visible to both rows (an interior tile): no comparisons.
-template <int NT, bool MASKED>
+// SHAPED: the scores pass the cap and lose the distance bias of `rs` (fp32 arithmetic; tanh as
+// 1 - 2 / (exp(2x) + 1), which is exact at both ends).
+template <int NT, bool MASKED, bool SHAPED = false>
 __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[HD / 8][4],
                                                float (&m)[2], float (&l)[2], int col0,
                                                const int (&lo)[2], const int (&hi)[2],
-                                               float scale_log2, int lane) {
+                                               float scale_log2, int lane,
+                                               const RowShape* rs = nullptr) {
   const int t = lane & 3;
   float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -175,6 +206,12 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[HD 
     for (int e = 0; e < 4; ++e) {
       const int i = e >> 1;
       float v = s[j][e] * scale_log2;
+      if (SHAPED) {
+        const int c = col0 + 8 * j + 2 * t + (e & 1);
+        if (rs->cap_l2 > 0.f)
+          v = rs->cap_l2 * (1.f - __fdividef(2.f, fast_exp2(s[j][e] * rs->k2) + 1.f));
+        v -= rs->slope[i] * (float)(rs->qpos[i] - c);
+      }
       if (MASKED) {
         const int c = col0 + 8 * j + 2 * t + (e & 1);
         v = (c >= lo[i] && c <= hi[i]) ? v : -INFINITY;

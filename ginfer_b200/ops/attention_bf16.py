@@ -77,7 +77,7 @@ def _scratch_for(nbytes: int, device) -> torch.Tensor:
 
 def decode(qkv, pages, block_table, cu_seqlens_q, positions, B, nh, nkv, hd, scale, window,
            page_size, splits, out=None, scratch=None, through_scratch=False, rope=None,
-           use_tma=True, stages=3, parts=1):
+           use_tma=True, stages=3, parts=1, softcap: float = 0.0, slopes=None):
     """Split-KV decode attention.  ``splits`` of 2, 4, 8 or 16 merge inside a thread-block cluster
     (no scratch memory) unless ``through_scratch``; any other number goes through scratch.
     ``rope = (table or None, rotary_dim, write)``: q and k arrive unrotated and the kernel
@@ -87,9 +87,15 @@ def decode(qkv, pages, block_table, cu_seqlens_q, positions, B, nh, nkv, hd, sca
     ring of ``stages`` tiles (2 .. 6; three let two CTAs share an SM, and with clusters of 8 only
     that fits a grid of 128 CTAs in one wave: four and six stages measured half as fast).
     ``parts`` > 1 (TMA kernel only): that many clusters share a request's keys and a second kernel
-    adds their results up (see :func:`decode_partition`)."""
+    adds their results up (see :func:`decode_partition`).
+    ``softcap`` > 0, ``slopes`` (fp32, a head): shaped scores as in ``ops.paged_attention_simt``;
+    they take the kernel that loads its tiles with ``cp.async`` (no rotation inside it)."""
     from . import _fn, _ok, _p, _stream
     defines = (f"GF_HEAD_DIM={hd}",)
+    is_shaped = bool(softcap) or slopes is not None
+    if is_shaped:
+        assert rope is None, "shaped scores and a rotation inside the kernel do not go together"
+        use_tma = False
     if out is None:
         out = torch.empty((qkv.shape[0], nh * hd), dtype=torch.bfloat16, device=qkv.device)
     if splits > 1 and scratch is None and (through_scratch or splits not in (2, 4, 8, 16)):
@@ -139,6 +145,16 @@ def decode(qkv, pages, block_table, cu_seqlens_q, positions, B, nh, nkv, hd, sca
               int(rot) if table is not None else 0, int(bool(write)), _stream()),
             "attn_decode_rope")
         return out
+    if is_shaped:
+        f = _fn("attention_bf16", "gf_attn_decode_shaped",
+                [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float,
+                 c_void_p, c_void_p], defines, kernels=1)
+        _ok(f(_p(qkv), qkv.stride(0), _p(pages[0]), _p(pages[1]), _p(block_table),
+              block_table.stride(0), _p(cu_seqlens_q), _p(positions), _p(out), _p(scratch), B, nh,
+              nkv, page_size, int(window), float(scale), int(splits), float(softcap or 0.0),
+              _p(slopes), _stream()), "attn_decode_shaped")
+        return out
     f = _fn("attention_bf16", "gf_attn_decode",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p], defines,
@@ -150,10 +166,20 @@ def decode(qkv, pages, block_table, cu_seqlens_q, positions, B, nh, nkv, hd, sca
 
 
 def prefill(qkv, pages, block_table, cu_seqlens_q, kv_lens, B, max_q_len, nh, nkv, hd, scale,
-            window, page_size, out=None):
+            window, page_size, out=None, softcap: float = 0.0, slopes=None):
     from . import _fn, _ok, _p, _stream
     if out is None:
         out = torch.empty((qkv.shape[0], nh * hd), dtype=torch.bfloat16, device=qkv.device)
+    if softcap or slopes is not None:
+        f = _fn("attention_bf16", "gf_attn_prefill_shaped",
+                [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p,
+                 c_void_p], (f"GF_HEAD_DIM={hd}",))
+        _ok(f(_p(qkv), qkv.stride(0), _p(pages[0]), _p(pages[1]), _p(block_table),
+              block_table.stride(0), _p(cu_seqlens_q), _p(kv_lens), _p(out), B, int(max_q_len), nh,
+              nkv, page_size, int(window), float(scale), float(softcap or 0.0), _p(slopes),
+              _stream()), "attn_prefill_shaped")
+        return out
     f = _fn("attention_bf16", "gf_attn_prefill",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
@@ -225,17 +251,17 @@ def try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window, page_size,
     ``window``: the mask as ``ops.mask_span`` gives it (negative: chunks)."""
     if not supports(hd, nh, nkv):
         return None
-    if softcap or slopes is not None:
-        return None          # TODO shaped scores
+    shape = dict(softcap=float(softcap or 0.0), slopes=slopes)
+    is_shaped = bool(softcap) or slopes is not None
     if ctx.decode_only:
         keys = min(abs(window), ctx.max_kv_len) if window else ctx.max_kv_len
         splits, parts = decode_partition(ctx.num_seqs, nh, nkv, keys)
         if ctx.extras.get("decode_splits"):
             splits, parts = ctx.extras["decode_splits"], 1
-        if not tma_serves(hd, page_size, splits):
+        if is_shaped or not tma_serves(hd, page_size, splits):
             parts = 1
         return decode(qkv, pages, block_table, ctx.cu_seqlens_q, ctx.positions, ctx.num_seqs, nh,
-                      nkv, hd, scale, window, page_size, splits, rope=rope, parts=parts)
+                      nkv, hd, scale, window, page_size, splits, rope=rope, parts=parts, **shape)
     assert rope is None, "only decode steps rotate inside the attention kernel"
     # A mixed step whose single tokens come first (as the scheduler orders them): those requests
     # go to the decode kernel, the portions behind them to a prefill kernel.  (A single token as a
@@ -250,13 +276,14 @@ def try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window, page_size,
         out = torch.empty((qkv.shape[0], nh * hd), dtype=torch.bfloat16, device=qkv.device)
         splits, parts = decode_partition(nd, nh, nkv, keys)
         decode(qkv, pages, block_table[:nd], None, ctx.positions, nd, nh, nkv, hd, scale, window,
-               page_size, splits, out=out, parts=parts if tma_serves(hd, page_size, splits) else 1)
+               page_size, splits, out=out,
+               parts=parts if tma_serves(hd, page_size, splits) and not is_shaped else 1, **shape)
         cu, kv_lens, table, B = cu[nd:], kv_lens[nd:], block_table[nd:], B - nd
         max_q = max(q_lens[nd:])
-    if max_q >= TC_MIN_QUERY_ROWS:
+    if max_q >= TC_MIN_QUERY_ROWS and not is_shaped:
         res = prefill_tc(qkv, pages, table, cu, kv_lens, B, max_q, nh, nkv, hd, scale, window,
                          page_size, out=out)
         if res is not None:
             return res
     return prefill(qkv, pages, table, cu, kv_lens, B, max_q, nh, nkv, hd, scale, window, page_size,
-                   out=out)
+                   out=out, **shape)

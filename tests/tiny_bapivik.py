@@ -17,8 +17,10 @@ from ginfer_b200.weights.safetensors_io import write_safetensors
 
 
 def attention(heads=4, kv_heads=2, dim=16, window=37, q_temp=(0.4, 16), softcap=15.0, scale=None):
+    # normed queries and keys: the scores' spread is set by the scale alone, and a scale of three
+    # times the usual one brings them under the cap's bend
     m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim,
-         "scale": scale if scale is not None else dim ** -0.5}
+         "scale": scale if scale is not None else 3.0 * dim ** -0.5}
     if window:
         m["mask"] = {"size": window}
     if q_temp:
@@ -116,8 +118,12 @@ def shaped_tensors(cfg: dict, seed: int) -> dict[str, torch.Tensor]:
         x = t[name]
         head, _, leaf = name.partition(".")
         kind = kinds.get(head)
-        if leaf in ("norm1", "norm2", "norm1b", "norm2b", "mix.norm", "mix.q.norm", "mix.k.norm",
-                    "mix.dq.norm", "mix.dkv.norm") or name == "final.norm":
+        if name == "final.norm":                         # logits that reach their cap's bend
+            t[name] = (1.0 + rnd(x, 0.3)) * 8.0
+        elif name == "embed":                            # tokens weigh more than positions
+            t[name] = x * 5.0
+        elif leaf in ("norm1", "norm2", "norm1b", "norm2b", "mix.norm", "mix.q.norm", "mix.k.norm",
+                      "mix.dq.norm", "mix.dkv.norm"):
             t[name] = 1.0 + rnd(x, 0.3)
         elif leaf == "dwa":                              # every earlier state counts
             w = 0.15 + 0.2 * torch.rand(x.shape, generator=g)
