@@ -161,15 +161,6 @@ __device__ __forceinline__ float fast_exp2(float x) {   // 2^x; -inf -> 0
   return y;
 }
 
-// Shaped scores.  With a cap, score <- cap * tanh(score / cap) after the scale; with slopes (one a
-// head), slope * (p - c) is then taken off the score of the key at c for the query at p.
-struct ScoreShape {
-  float cap;              // 0: no cap
-  const float* slopes;    // [heads], or null: no distance bias
-};
-__device__ __forceinline__ bool shaped(const ScoreShape& sh) {
-  return sh.cap > 0.f || sh.slopes != nullptr;
-}
 // What a thread needs of the shape for its two rows, in log2 units.
 struct RowShape {
   float k2;               // 2 log2(e) scale / cap: exp(2 x / cap) = 2^(k2 dot)

@@ -351,6 +351,9 @@ struct Item {
   int b, head, r0, rows, q_begin, pos0, key_lo, p_last, j0, ntiles, kvh;
 };
 
+// SHAPED: the scores pass the cap and the distance bias of `shape` (a kernel of its own, so that
+// the plain one keeps its registers).
+template <bool SHAPED>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
                        const __grid_constant__ CUtensorMap tmap_k,
@@ -359,7 +362,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
                        const int* __restrict__ cu_seqlens_q, const int* __restrict__ kv_lens,
                        bf16* __restrict__ out, int nh, int nkv, int page_size, int window,
                        float scale_log2, int oob_row, int q_tiles, int B,
-                       int* __restrict__ err, long long* __restrict__ dbg) {
+                       int* __restrict__ err, long long* __restrict__ dbg,
+                       const ScoreShape shape) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // the kernel has no static shared memory, so the dynamic part starts at the aligned base; the
   // swizzled tiles need that (checked below: a misaligned base ends the CTA with an error code)
@@ -698,6 +702,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       const int lo = first_visible_key(p, window);
       const int wp0 = pos00 + qd * 32;                         // position of the warp's first row
       const bool tr = r == 0;
+      // shaped scores, in log2 units: exp(2 x / cap) = 2^(k2 dot); what follows multiplies by
+      // scale_log2 again, so the shaped score is handed on divided by it
+      const float cap_l2 = SHAPED && shape.cap > 0.f ? shape.cap * LOG2E : 0.f;
+      const float k2 = SHAPED && shape.cap > 0.f ? 2.f * scale_log2 / shape.cap : 0.f;
+      const float slope_l2 = SHAPED && shape.slopes ? shape.slopes[head] * LOG2E : 0.f;
+      const float inv_scale_l2 = 1.f / scale_log2;
       float m_used = -INFINITY;        // the maximum the accumulated P and l are scaled by
       float l = 0.f;                   // the row sum
       for (int t = 0; t < mine; ++t, ++cnt) {
@@ -718,6 +728,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
         for (int cc = 0; cc < KT / 32; ++cc)
           tmem_ld32(my_s + 32 * cc, *reinterpret_cast<float(*)[32]>(v + 32 * cc));
         tmem_ld_wait();
+        if (SHAPED) {
+          // cap (tanh as 1 - 2 / (exp(2x) + 1), exact at both ends) and distance bias, fp32
+          const float dist0 = (float)(p - col0);
+#pragma unroll
+          for (int k = 0; k < KT; ++k) {
+            float x = v[k] * scale_log2;
+            if (cap_l2 > 0.f)
+              x = cap_l2 * (1.f - __fdividef(2.f, fast_exp2(v[k] * k2) + 1.f));
+            v[k] = (x - slope_l2 * (dist0 - (float)k)) * inv_scale_l2;
+          }
+        }
         if (!interior) {
 #pragma unroll
           for (int k = 0; k < KT; ++k) {
@@ -907,12 +928,12 @@ GF_EXPORT int gf_attn_tc_head_dim() { return HD; }
 // q: T rows of q_row_stride elements whose first nh * HD hold the query heads; kpages / vpages:
 // [num_pages, page_size, nkv, HD]; out [T, nh, HD].  Returns -6 for what it cannot serve (page
 // sizes that are not a multiple of 8 or do not divide 128, unaligned pointers or strides).
-GF_EXPORT int gf_attn_prefill_tc(const void* q, int q_row_stride, const void* kpages,
-                                 const void* vpages, int num_pages, const int* block_table,
-                                 int table_stride, const int* cu_seqlens_q, const int* kv_lens,
-                                 void* out, int T, int B, int max_q_len, int nh, int nkv,
-                                 int page_size, int window, float scale, int* err, void* dbg,
-                                 void* stream) {
+static int attn_prefill_tc_impl(const void* q, int q_row_stride, const void* kpages,
+                                const void* vpages, int num_pages, const int* block_table,
+                                int table_stride, const int* cu_seqlens_q, const int* kv_lens,
+                                void* out, int T, int B, int max_q_len, int nh, int nkv,
+                                int page_size, int window, float scale, int* err, void* dbg,
+                                void* stream, const ScoreShape shape) {
   if (B <= 0 || max_q_len <= 0 || T <= 0) return 0;
   if (nh % nkv || page_size % 8 || KT % page_size || page_size > KT) return -6;
   if (q_row_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)kpages & 15) ||
@@ -927,7 +948,10 @@ GF_EXPORT int gf_attn_prefill_tc(const void* q, int q_row_stride, const void* kp
   const size_t smem = Q_BYTES + K_STAGES * K_BYTES + V_STAGES * V_BYTES + sizeof(Barriers);
   static OncePerDevice attrs;
   if (int rc = attrs.run([&] {
-        return cudaFuncSetAttribute(attn_prefill_tc_kernel,
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<false>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        return cudaFuncSetAttribute(attn_prefill_tc_kernel<true>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       }))
     return rc;
@@ -939,8 +963,41 @@ GF_EXPORT int gf_attn_prefill_tc(const void* q, int q_row_stride, const void* kp
       cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
     sms = v;
   dim3 grid((unsigned)(items < sms ? items : sms));
-  return launch_kernel(attn_prefill_tc_kernel, grid, dim3(NTHREADS), smem, (cudaStream_t)stream,
-                       mq, mk, mv, block_table, table_stride, cu_seqlens_q, kv_lens, (bf16*)out,
-                       nh, nkv, page_size, window, scale * LOG2E, (int)slots, q_tiles, B, err,
-                       (long long*)dbg);
+  if (shaped(shape))
+    return launch_kernel(attn_prefill_tc_kernel<true>, grid, dim3(NTHREADS), smem,
+                         (cudaStream_t)stream, mq, mk, mv, block_table, table_stride, cu_seqlens_q,
+                         kv_lens, (bf16*)out, nh, nkv, page_size, window, scale * LOG2E, (int)slots,
+                         q_tiles, B, err, (long long*)dbg, shape);
+  return launch_kernel(attn_prefill_tc_kernel<false>, grid, dim3(NTHREADS), smem,
+                       (cudaStream_t)stream, mq, mk, mv, block_table, table_stride, cu_seqlens_q,
+                       kv_lens, (bf16*)out, nh, nkv, page_size, window, scale * LOG2E, (int)slots,
+                       q_tiles, B, err, (long long*)dbg, shape);
+}
+
+GF_EXPORT int gf_attn_prefill_tc(const void* q, int q_row_stride, const void* kpages,
+                                 const void* vpages, int num_pages, const int* block_table,
+                                 int table_stride, const int* cu_seqlens_q, const int* kv_lens,
+                                 void* out, int T, int B, int max_q_len, int nh, int nkv,
+                                 int page_size, int window, float scale, int* err, void* dbg,
+                                 void* stream) {
+  return attn_prefill_tc_impl(q, q_row_stride, kpages, vpages, num_pages, block_table,
+                              table_stride, cu_seqlens_q, kv_lens, out, T, B, max_q_len, nh, nkv,
+                              page_size, window, scale, err, dbg, stream,
+                              ScoreShape{0.f, nullptr});
+}
+
+// The same with shaped scores: `softcap` > 0 caps them (cap * tanh(score / cap)); `slopes` (fp32
+// [nh] or null) takes slope * (p - c) off the score of the key at c for the query at p.
+GF_EXPORT int gf_attn_prefill_tc_shaped(const void* q, int q_row_stride, const void* kpages,
+                                        const void* vpages, int num_pages, const int* block_table,
+                                        int table_stride, const int* cu_seqlens_q,
+                                        const int* kv_lens, void* out, int T, int B, int max_q_len,
+                                        int nh, int nkv, int page_size, int window, float scale,
+                                        float softcap, const float* slopes, int* err, void* dbg,
+                                        void* stream) {
+  if (softcap < 0.f) return -3;
+  return attn_prefill_tc_impl(q, q_row_stride, kpages, vpages, num_pages, block_table,
+                              table_stride, cu_seqlens_q, kv_lens, out, T, B, max_q_len, nh, nkv,
+                              page_size, window, scale, err, dbg, stream,
+                              ScoreShape{softcap, slopes});
 }

@@ -97,6 +97,17 @@ __host__ __device__ __forceinline__ int first_visible_key(int p, int span) {
   return 0;
 }
 
+// Shaped attention scores.  With a cap, score <- cap * tanh(score / cap) after the scale; with
+// slopes (one a head), slope * (p - c) is then taken off the score of the key at c for the query at
+// p.  32-bit arithmetic in every kernel that takes it.
+struct ScoreShape {
+  float cap;              // 0: no cap
+  const float* slopes;    // [heads], or null: no distance bias
+};
+__host__ __device__ __forceinline__ bool shaped(const ScoreShape& sh) {
+  return sh.cap > 0.f || sh.slopes != nullptr;
+}
+
 // ---- programmatic dependent launch -------------------------------------------------------------
 // A kernel launched with the attribute may start while its predecessor in the stream still runs;
 // it must call pdl_wait() before it reads (or overwrites) anything the predecessor touches, and

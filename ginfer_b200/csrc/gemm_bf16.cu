@@ -49,6 +49,9 @@ namespace gf {
 
 constexpr int NTHREADS = 192;
 constexpr int EPI_STORE = 0, EPI_SILU = 2, EPI_RESID = 3;
+// (callers may also ask for 1: EPI_STORE whose result, bias included, passes relu(x)^2; the
+// kernel is the same instance and takes the activation as GemmExtra::act)
+constexpr int EPI_RELU2_CODE = 1;
 
 struct GemmExtra {
   // consumer of a deferred RMS normalisation: scale[m] = rsqrt(sum_p in_sumsq[p][m] * inv_k + eps)
@@ -63,7 +66,13 @@ struct GemmExtra {
   const void* gamma;         // [N], bf16 or fp32
   int gamma_f32;
   float* out_sumsq;          // [parts][ss_ld]; part = tile of rows (* splits + split)
+  // EPI_STORE
+  int act;                   // 1: the result (with its bias) passes relu(x)^2 before it is stored
 };
+__device__ __forceinline__ float relu2(float x) {
+  x = fmaxf(x, 0.f);
+  return x * x;
+}
 constexpr int kMaxTiles = 1 << 16;
 __device__ unsigned int g_tile_done[kMaxTiles];
 
@@ -137,7 +146,9 @@ __device__ __forceinline__ void epilogue16(float (&v)[16], OUT* __restrict__ out
     if (n < N) {
 #pragma unroll
       for (int j = 0; j < 16; ++j)
-        if (m_base + j < M) store_out<OUT>(out + (size_t)(m_base + j) * ldo + n, v[j] + b);
+        if (m_base + j < M)
+          store_out<OUT>(out + (size_t)(m_base + j) * ldo + n,
+                         ex.act ? relu2(v[j] + b) : v[j] + b);
     }
   } else if (EPI == EPI_RESID) {
     const float b = (bias && n < N) ? bias[n] : 0.f;
@@ -321,6 +332,16 @@ __device__ __forceinline__ void cluster_reduce(uint32_t red, const float* recv, 
                   store_out<OUT>(out + at + j, v[j]);
                   if (ex.out_scaled) ex.out_scaled[at + j] = __float2bfloat16_rn(g[j]);
                 }
+            }
+          } else if (EPI == EPI_STORE && ex.act) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = relu2(v[j]);
+            if (vec) {
+              store4(out + at, v);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (n + j < N) store_out<OUT>(out + at + j, v[j]);
             }
           } else if (vec) {
             store4(out + at, v);
@@ -900,6 +921,8 @@ GF_EXPORT int gf_gemm_bf16_tc_ex(const void* x, int ldx, const void* w, const fl
                                  int gamma_f32, float* out_sumsq) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return -6;
+  const int act = epi == EPI_RELU2_CODE ? 1 : 0;
+  if (act) epi = EPI_STORE;
   if (epi == EPI_SILU && ((N & 1) || out_f32)) return -6;
   if (epi != EPI_STORE && epi != EPI_SILU && epi != EPI_RESID) return -6;
   const int bn = gf_gemm_bf16_token_tile(M);
@@ -928,6 +951,7 @@ GF_EXPORT int gf_gemm_bf16_tc_ex(const void* x, int ldx, const void* w, const fl
   ex.gamma = gamma;
   ex.gamma_f32 = gamma_f32;
   ex.out_sumsq = out_sumsq;
+  ex.act = act;
   auto st = (cudaStream_t)stream;
   float* ws = (float*)workspace;
   if (epi == EPI_SILU)

@@ -201,13 +201,16 @@ POLY_EXP_EVERY = int(os.environ.get("GINFER_B200_ATTN_POLY_EXP") or 0)
 
 
 def prefill_tc(qkv, pages, block_table, cu_seqlens_q, kv_lens, B, max_q_len, nh, nkv, hd, scale,
-               window, page_size, trace=None, out=None, poly_exp_every: int | None = None):
+               window, page_size, trace=None, out=None, poly_exp_every: int | None = None,
+               softcap: float = 0.0, slopes=None):
     """Prefill attention on tcgen05 (``csrc/attention_tc.cu``); ``None`` if it cannot serve the
     shapes.  ``trace``: an int64 tensor of ``768 + 4 * CTAs`` slots that receives clock stamps of
     the first CTA's phases ([role 0 softmax (by tile), 1 MMA (by a stream's tile), 2 loader][32][8])
     and, behind them, every CTA's (start ns, end ns, SM) (for tuning; compiled into a build of its
     own).
-    ``poly_exp_every``: see ``POLY_EXP_EVERY`` (``None``: that default)."""
+    ``poly_exp_every``: see ``POLY_EXP_EVERY`` (``None``: that default).
+    ``softcap`` > 0, ``slopes`` (fp32, a head): shaped scores as in ``ops.paged_attention_simt``
+    (an instance of the kernel of its own)."""
     from ctypes import c_float, c_int, c_void_p
 
     from . import _fn, _ok, _p, _stream
@@ -221,14 +224,25 @@ def prefill_tc(qkv, pages, block_table, cu_seqlens_q, kv_lens, B, max_q_len, nh,
     defines = (f"GF_HEAD_DIM={hd}",) + ((f"GF_POLY_EXP_EVERY={every}",) if every > 0 else ())
     if trace is not None:
         defines += ("GF_TRACE",)          # a build of its own: the phase stamps cost the issuing thread time
-    f = _fn("attention_tc", "gf_attn_prefill_tc",
-            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-             c_void_p, c_void_p], defines)
-    rc = f(_p(qkv), qkv.stride(0), _p(pages[0]), _p(pages[1]), pages.shape[1], _p(block_table),
-           block_table.stride(0), _p(cu_seqlens_q), _p(kv_lens), _p(out), T, B, int(max_q_len),
-           nh, nkv, page_size, int(window), float(scale), _p(_dev_state(qkv.device)["err"]),
-           _p(trace), _stream())
+    if softcap or slopes is not None:
+        f = _fn("attention_tc", "gf_attn_prefill_tc_shaped",
+                [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                 c_void_p, c_void_p, c_void_p, c_void_p], defines)
+        rc = f(_p(qkv), qkv.stride(0), _p(pages[0]), _p(pages[1]), pages.shape[1],
+               _p(block_table), block_table.stride(0), _p(cu_seqlens_q), _p(kv_lens), _p(out), T,
+               B, int(max_q_len), nh, nkv, page_size, int(window), float(scale),
+               float(softcap or 0.0), _p(slopes), _p(_dev_state(qkv.device)["err"]), _p(trace),
+               _stream())
+    else:
+        f = _fn("attention_tc", "gf_attn_prefill_tc",
+                [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                 c_void_p, c_void_p], defines)
+        rc = f(_p(qkv), qkv.stride(0), _p(pages[0]), _p(pages[1]), pages.shape[1],
+               _p(block_table), block_table.stride(0), _p(cu_seqlens_q), _p(kv_lens), _p(out), T,
+               B, int(max_q_len), nh, nkv, page_size, int(window), float(scale),
+               _p(_dev_state(qkv.device)["err"]), _p(trace), _stream())
     if rc == -6:
         return None
     _ok(rc, "attn_prefill_tc")
@@ -280,9 +294,9 @@ def try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window, page_size,
                parts=parts if tma_serves(hd, page_size, splits) and not is_shaped else 1, **shape)
         cu, kv_lens, table, B = cu[nd:], kv_lens[nd:], block_table[nd:], B - nd
         max_q = max(q_lens[nd:])
-    if max_q >= TC_MIN_QUERY_ROWS and not is_shaped:
+    if max_q >= TC_MIN_QUERY_ROWS:
         res = prefill_tc(qkv, pages, table, cu, kv_lens, B, max_q, nh, nkv, hd, scale, window,
-                         page_size, out=out)
+                         page_size, out=out, **shape)
         if res is not None:
             return res
     return prefill(qkv, pages, table, cu, kv_lens, B, max_q, nh, nkv, hd, scale, window, page_size,

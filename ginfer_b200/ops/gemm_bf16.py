@@ -111,7 +111,8 @@ def sumsq_ld(M: int) -> int:
 
 def gemm(x, weight, bias_f32=None, out_dtype=torch.bfloat16, epi: int = 0, split_k=None,
          through_workspace: bool = False, scale: RowScale | None = None, resid=None, gamma=None):
-    """``x [M, K] @ weight[N, K]^T``; ``epi`` 0: (+ bias) -> ``[M, N]``; ``epi`` 2: weight rows
+    """``x [M, K] @ weight[N, K]^T``; ``epi`` 0: (+ bias) -> ``[M, N]``; ``epi`` 1: the same
+    through ``relu(.)^2``; ``epi`` 2: weight rows
     are interleaved (gate_i, up_i) and the result is ``silu(gate) * up`` -> ``[M, N / 2]``.
     ``split_k``: None picks it; 2, 4, 8 or 12 add up inside a cluster; with ``through_workspace``
     any number of splits adds up through global memory.  ``scale``: the accumulator of every token
@@ -185,12 +186,13 @@ def plain_limit(weight) -> int:
     return PLAIN_MAX_TOKENS_LONG_K if weight.shape[1] >= LONG_K else PLAIN_MAX_TOKENS
 
 
-def try_linear(x, weight, bias_f32, out_dtype):
+def try_linear(x, weight, bias_f32, out_dtype, relu2: bool = False):
     """Run the tcgen05 kernel where it is the faster one (the small batches of decode steps and
-    short prompt portions); ``None`` hands the product to cuBLAS."""
+    short prompt portions); ``None`` hands the product to cuBLAS.  ``relu2``: the result passes
+    ``relu(.)^2`` in the kernel's epilogue."""
     if x.shape[0] > plain_limit(weight):
         return None
-    return gemm(x, weight, bias_f32, out_dtype, epi=0)
+    return gemm(x, weight, bias_f32, out_dtype, epi=1 if relu2 else 0)
 
 
 # Plain products leave for cuBLAS above this many tokens.  In a CUDA graph on a B200, 1.5B shapes,

@@ -34,11 +34,15 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, bias=None) -> torch.Tensor:
 
 class Linear:
     """``y = x W^T + b``.  ``out_dtype`` float32 asks for fp32 results from bf16 operands (the
-    output head)."""
+    output head).  ``activation="relu2"``: ``y = relu(x W^T + b)^2``, in the product's epilogue
+    where the tcgen05 kernel runs it (few tokens), else in a kernel behind the library's."""
 
     def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None = None,
-                 out_dtype: torch.dtype | None = None):
+                 out_dtype: torch.dtype | None = None, activation: str | None = None):
         _cuda(weight, bias)
+        if activation not in (None, "relu2"):
+            raise ValueError(f"activation {activation!r}: only 'relu2' is there")
+        self.activation = activation
         self.weight = weight.contiguous()
         self.bias = bias
         self.out_features, self.in_features = weight.shape
@@ -55,6 +59,18 @@ class Linear:
             raise TypeError(f"Linear takes float32 or bfloat16 weights, not {self.dtype}")
 
     def __call__(self, x) -> torch.Tensor:
+        if self.activation is None:
+            return self._product(x)
+        if (self.dtype == torch.bfloat16 and not hasattr(x, "materialize")
+                and x.dtype == self.dtype):
+            from . import gemm_bf16
+            y = gemm_bf16.try_linear(x, self.weight, self._bias_f32, self.out_dtype, relu2=True)
+            if y is not None:
+                return y
+        from . import activation_
+        return activation_(self._product(x), self.activation)
+
+    def _product(self, x) -> torch.Tensor:
         if hasattr(x, "materialize"):                 # a normalisation not computed yet
             if self.dtype == torch.bfloat16 and x.scaled is not None:
                 from . import gemm_bf16

@@ -107,11 +107,11 @@ class DenseActivationMLP(FeedForward):
 
     def load(self, tensors, dtype, device):
         b = (lambda k: tensors[k + ".b"].float().contiguous()) if self.bias else (lambda k: None)
-        self.up = ops.Linear(tensors[self.up_key], b(self.up_key))
+        self.up = ops.Linear(tensors[self.up_key], b(self.up_key), activation=self.activation)
         self.down = ops.Linear(tensors[self.down_key], b(self.down_key), out_dtype=torch.float32)
 
     def forward(self, x, ctx):
-        return self.down(ops.activation_(self.up(x), self.activation))
+        return self.down(self.up(x))
 
 
 register_feed_forward("dense_mlp", DenseActivationMLP)

@@ -590,7 +590,8 @@ def _shaped_reference(q, k, v, p, nh, nkv, scale, window, cap, slopes):
 def test_attention_with_capped_scores_and_a_distance_bias(dtype, nh, nkv, D, window, cap, sloped):
     """The step's queries over a paged cache in shuffled pages, with a cap on the scores and a
     bias a head by the distance: every row of a prompt (the tensor-core prompt kernel in bfloat16
-    where the head size allows, the fp32-arithmetic kernel elsewhere), single decoded rows of
+    where the head size allows: tcgen05 from 64 rows, ``mma.sync`` below; the fp32-arithmetic
+    kernel elsewhere), single decoded rows of
     several requests (the split decode kernel), and single rows in front of a portion."""
     from ginfer_b200 import ops
     g = torch.Generator().manual_seed(D + window)
@@ -627,5 +628,33 @@ def test_attention_with_capped_scores_and_a_distance_bias(dtype, nh, nkv, D, win
             assert torch.allclose(out[i], want, atol=tol, rtol=tol), (p, starts)
     run([list(range(keys))], "prompt")                                   # a whole prompt
     run([list(range(130, keys))], "portion")                             # a later portion
+    run([list(range(150, keys))], "short portion")                       # under the tcgen05 kernel's rows
     run([[keys - 1], [5], [window if window else 63], [0], [77]], "decode")
     run([[keys - 1], [40], list(range(90, 175))], "mixed")               # single rows, then a portion
+
+
+@pytest.mark.parametrize("M", [1, 8, 16, 33, 64, 100, 700])
+def test_squared_relu_in_the_products_epilogue(M):
+    """``relu(x W^T + b)^2`` from the tcgen05 kernel (direct tiles and K splits added up inside a
+    cluster, by the token count) and from the library product with the kernel behind it, rows of
+    exactly zero and negative ones included; in 32-bit from the FMA product."""
+    from ginfer_b200 import ops
+    from ginfer_b200.ops import gemm_bf16
+    g = torch.Generator(device="cuda").manual_seed(M)
+    for K, N in ((192, 328), (4096, 136), (64, 1000)):
+        x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(N, K, generator=g, device="cuda") * 0.2).to(torch.bfloat16)
+        w[:5] = 0
+        b = torch.randn(N, generator=g, device="cuda")
+        b[:3] = 0
+        for bias in (b, None):
+            want = torch.relu(x.double() @ w.double().T + (bias.double() if bias is not None else 0)) ** 2
+            for out in (torch.bfloat16, torch.float32):
+                y = ops.Linear(w, bias, out_dtype=out, activation="relu2")(x)
+                assert y.dtype == out and y.shape == (M, N)
+                tol = 0.02 if out == torch.bfloat16 else 2e-3
+                assert float((y.double() - want).abs().max()) <= tol * float(want.abs().max())
+                assert float(y[:, :3].abs().max()) == 0.0 or bias is not None
+            y32 = ops.Linear(w.float(), bias, activation="relu2")(x.float())
+            assert torch.allclose(y32.double(), want, atol=1e-3, rtol=1e-4)
+    gemm_bf16.check_errors("cuda:0")
