@@ -477,7 +477,7 @@ def run_design(args) -> int:
 # ----------------------------------------------------------------------------- small workloads
 MICRO = ("gemm_gateup_m8", "gemm_down_m8", "gemm_lmhead_m8", "gemm_gateup_m2048", "gemm_qkv_m2048",
          "attn_decode_b8",
-         "attn_decode_b64", "attn_decode_b1_ctx32768", "prefill_2layers")
+         "attn_decode_b64", "attn_decode_b1_ctx32768", "prefill_2layers", "bapivik_prefill_4layers")
 
 
 def run_micro(name: str) -> int:
@@ -561,6 +561,21 @@ def run_micro(name: str) -> int:
         eng = Engine(config=cfg, dtype="bfloat16", max_num_seqs=4, max_seq_len=CONTEXT,
                      num_kvcache_blocks=PREFILL_TOKENS // PAGE + 64, enforce_eager=True)
         prompt = torch.randint(0, V, (PREFILL_TOKENS,)).tolist()
+        for _ in range(3):
+            eng.runner.step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
+            eng.runner.end("p")
+        torch.cuda.synchronize()
+        print(json.dumps({"micro": name, "tokens": PREFILL_TOKENS}))
+        return 0
+    if name == "bapivik_prefill_4layers":
+        # one turn of Bapivik's four layers at size m, a 2,048-token prompt three times
+        from ginfer_b200.engine import StepEntry
+        from ginfer_b200.engine.llm import Engine
+        cfg = design_configs("bapivik", "m", 4)["bapivik"]
+        eng = Engine(config=cfg, weights_seed=0, dtype="bfloat16", max_num_seqs=4,
+                     max_seq_len=CONTEXT, kvcache_block_size=PAGE,
+                     num_kvcache_blocks=PREFILL_TOKENS // PAGE + 64, enforce_eager=True)
+        prompt = torch.randint(0, cfg["vocab"], (PREFILL_TOKENS,)).tolist()
         for _ in range(3):
             eng.runner.step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
             eng.runner.end("p")

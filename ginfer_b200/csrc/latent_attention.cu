@@ -82,38 +82,92 @@ __global__ void latent_prepare_kernel(const T* __restrict__ qd, int ld, int H, i
 // RMS-normed with qw into cq, in the activation type, for the query up-projection) and the key/value
 // latent (C channels from c_col, RMS-normed with cw into the token's cache slot).  Either may be
 // absent (Q = 0; slot_mapping null).  One block a token.
-template <typename T>
+// Two channels an access: a pair of T as two floats, and back.
+__device__ __forceinline__ float2 load_pair(const float* p) {
+  return *reinterpret_cast<const float2*>(p);
+}
+__device__ __forceinline__ float2 load_pair(const bf16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+__device__ __forceinline__ void store_pair(float* p, float a, float b) {
+  *reinterpret_cast<float2*>(p) = make_float2(a, b);
+}
+__device__ __forceinline__ void store_pair(bf16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+// PAIRS: every column offset and count is even and the rows are aligned for pairs.  The two sums
+// of squares are reduced together (one pass of barriers for both norms).
+template <typename T, bool PAIRS>
 __global__ void latent_norms_kernel(const T* __restrict__ proj, int ld, int q_col, int Q,
                                     const float* __restrict__ qw, T* __restrict__ cq, int c_col,
                                     int C, const float* __restrict__ cw, float eps,
                                     const int* __restrict__ slot_mapping, T* __restrict__ c_pages) {
-  __shared__ float scratch[33];
+  __shared__ float scratch[2][33];
   const int t = blockIdx.x;
   pdl_trigger();
   pdl_wait();
   const T* row = proj + (size_t)t * ld;
-  if (Q > 0) {
-    float ss = 0.f;
-    for (int j = threadIdx.x; j < Q; j += blockDim.x) {
+  const bool write_c = slot_mapping != nullptr && C > 0;
+  const int Cn = write_c ? C : 0;
+  constexpr int W = PAIRS ? 2 : 1;
+  float ssq = 0.f, ssc = 0.f;
+  for (int j = threadIdx.x * W; j < Q; j += blockDim.x * W) {
+    if (PAIRS) {
+      const float2 v = load_pair(row + q_col + j);
+      ssq += v.x * v.x + v.y * v.y;
+    } else {
       const float v = to_f32(row[q_col + j]);
-      ss += v * v;
+      ssq += v * v;
     }
-    ss = block_sum(ss, scratch);
-    const float rms = sqrtf(ss / (float)Q + eps);
-    for (int j = threadIdx.x; j < Q; j += blockDim.x)
-      cq[(size_t)t * Q + j] = from_f32<T>(to_f32(row[q_col + j]) / rms * qw[j]);
   }
-  if (slot_mapping != nullptr && C > 0) {
-    float ss = 0.f;
-    for (int j = threadIdx.x; j < C; j += blockDim.x) {
+  for (int j = threadIdx.x * W; j < Cn; j += blockDim.x * W) {
+    if (PAIRS) {
+      const float2 v = load_pair(row + c_col + j);
+      ssc += v.x * v.x + v.y * v.y;
+    } else {
       const float v = to_f32(row[c_col + j]);
-      ss += v * v;
+      ssc += v * v;
     }
-    ss = block_sum(ss, scratch);
-    const float rms = sqrtf(ss / (float)C + eps);
+  }
+  {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    ssq = warp_sum(ssq);
+    ssc = warp_sum(ssc);
+    if (lane == 0) scratch[0][warp] = ssq, scratch[1][warp] = ssc;
+    __syncthreads();
+    if (warp < 2) {
+      float v = lane < nwarps ? scratch[warp][lane] : 0.f;
+      v = warp_sum(v);
+      if (lane == 0) scratch[warp][32] = v;
+    }
+    __syncthreads();
+    ssq = scratch[0][32];
+    ssc = scratch[1][32];
+  }
+  if (Q > 0) {
+    const float inv = 1.f / sqrtf(ssq / (float)Q + eps);
+    T* dst = cq + (size_t)t * Q;
+    for (int j = threadIdx.x * W; j < Q; j += blockDim.x * W) {
+      if (PAIRS) {
+        const float2 v = load_pair(row + q_col + j);
+        store_pair(dst + j, v.x * inv * qw[j], v.y * inv * qw[j + 1]);
+      } else {
+        dst[j] = from_f32<T>(to_f32(row[q_col + j]) * inv * qw[j]);
+      }
+    }
+  }
+  if (write_c) {
+    const float inv = 1.f / sqrtf(ssc / (float)C + eps);
     T* dst = c_pages + (size_t)slot_mapping[t] * C;
-    for (int j = threadIdx.x; j < C; j += blockDim.x)
-      dst[j] = from_f32<T>(to_f32(row[c_col + j]) / rms * cw[j]);
+    for (int j = threadIdx.x * W; j < C; j += blockDim.x * W) {
+      if (PAIRS) {
+        const float2 v = load_pair(row + c_col + j);
+        store_pair(dst + j, v.x * inv * cw[j], v.y * inv * cw[j + 1]);
+      } else {
+        dst[j] = from_f32<T>(to_f32(row[c_col + j]) * inv * cw[j]);
+      }
+    }
   }
 }
 
@@ -542,12 +596,19 @@ GF_EXPORT int gf_latent_norms(const void* proj, int ld, int q_col, int Q, const 
   auto st = (cudaStream_t)stream;
   const int widest = Q > C ? Q : C;
   const dim3 grid(T), block(widest > 512 ? 256 : 128);
-  if (dtype == GF_F32)
-    return launch_kernel(latent_norms_kernel<float>, grid, block, 0, st, (const float*)proj, ld,
-                         q_col, Q, qw, (float*)cq, c_col, C, cw, eps, slot_mapping,
-                         (float*)c_pages);
-  return launch_kernel(latent_norms_kernel<bf>, grid, block, 0, st, (const bf*)proj, ld, q_col, Q,
-                       qw, (bf*)cq, c_col, C, cw, eps, slot_mapping, (bf*)c_pages);
+  const size_t esz = dtype == GF_F32 ? 4 : 2;
+  const bool pairs = !((ld | q_col | Q | c_col | C) & 1) && (uintptr_t)proj % (2 * esz) == 0 &&
+                     (uintptr_t)cq % (2 * esz) == 0 && (uintptr_t)c_pages % (2 * esz) == 0;
+#define GF_NORMS(TT, P)                                                                        \
+  return launch_kernel(latent_norms_kernel<TT, P>, grid, block, 0, st, (const TT*)proj, ld,     \
+                       q_col, Q, qw, (TT*)cq, c_col, C, cw, eps, slot_mapping, (TT*)c_pages)
+  if (dtype == GF_F32) {
+    if (pairs) GF_NORMS(float, true);
+    GF_NORMS(float, false);
+  }
+  if (pairs) GF_NORMS(bf, true);
+  GF_NORMS(bf, false);
+#undef GF_NORMS
 }
 
 GF_EXPORT int gf_latent_attention(const float* q_lat, const float* q_rot, const void* c_pages,

@@ -586,7 +586,8 @@ def _shaped_reference(q, k, v, p, nh, nkv, scale, window, cap, slopes):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh, nkv, D, window, cap, sloped", [
     (4, 2, 64, 100, 25.0, True), (2, 2, 64, 48, 0.0, True), (16, 4, 128, 0, 30.0, True),
-    (3, 1, 16, 37, 4.0, False), (6, 2, 24, 19, 15.0, True), (20, 1, 64, 70, 10.0, True)])
+    (3, 1, 16, 37, 4.0, False), (6, 2, 24, 19, 15.0, True), (20, 1, 64, 70, 10.0, True),
+    (4, 2, 48, 33, 20.0, True), (2, 2, 80, 72, 20.0, True)])
 def test_attention_with_capped_scores_and_a_distance_bias(dtype, nh, nkv, D, window, cap, sloped):
     """The step's queries over a paged cache in shuffled pages, with a cap on the scores and a
     bias a head by the distance: every row of a prompt (the tensor-core prompt kernel in bfloat16
