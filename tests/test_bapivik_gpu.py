@@ -91,7 +91,7 @@ def row_errors(rows, want):
 # float32: differences of summation order.  bfloat16: the folders' peaked attention amplifies the
 # format's rounding, so single rows may be off (at most one in thirty) while the mean stays small;
 # a misplaced page, a lost state or a window off by one puts most rows near one.
-LIMIT = {"float32": (3e-4, 5e-5), "bfloat16": (0.3, 0.1)}
+LIMIT = {"float32": (1e-4, 2e-5), "bfloat16": (0.3, 0.05)}
 
 
 def check(rows, want, dtype, requests):
@@ -128,7 +128,7 @@ def test_the_oracle_without_a_mechanism_is_far_from_the_oracle(tmp_path_factory,
     full = expected(d, cfg, reqs)["r0"]
     less = expected(d, cfg, reqs, without=(without,))["r0"]
     rows = {("r0", p): less[p].astype(np.float32) for p in range(40, 90)}
-    assert row_errors(rows, {"r0": full})[2] > 0.01        # the float32 limit is 3e-4
+    assert row_errors(rows, {"r0": full})[2] > 0.01        # the float32 limit is 1e-4
 
 
 # ----------------------------------------------------------------------------- cuts of the same work
@@ -144,7 +144,7 @@ def cuts(reqs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["MIXED", "OTHER", "WIDE"])
+@pytest.mark.parametrize("name", ["MIXED", "OTHER", "WIDE", "ODD"])
 def test_cuts_agree_with_plain(tmp_path_factory, name, dtype):
     cfg = getattr(tb, name)
     d = folder(tmp_path_factory, name, cfg, dtype)

@@ -97,6 +97,16 @@ WIDE = config([
     layer(latent(heads=2, dim=32, vdim=64, kv_rank=64, q_rank=32, kv_from=1), dense(ff=64)),
 ], width=128, vocab=197, eps=1e-5, max_positions=700, logit_softcap=20.0)
 
+# a width that is no multiple of four and sizes that are no multiple of eight anywhere: the scalar
+# paths of the row kernels and the products that leave for the library
+ODD = config([
+    layer(lightning(heads=2, dim=12, vdim=9, decay=(0.9, 0.99)), dense(ff=37)),
+    layer(latent(heads=3, dim=10, vdim=7, kv_rank=18, q_rank=11), dense(ff=50)),
+    layer(attention(heads=3, kv_heads=1, dim=14, window=21), None),
+    layer(latent(heads=2, dim=6, vdim=5, kv_rank=18, q_rank=9, kv_from=1), dense(ff=20)),
+    layer(attention(heads=2, kv_heads=2, dim=16, window=40, softcap=None), dense(ff=33)),
+], width=50, vocab=101, eps=1e-5, max_positions=200, logit_softcap=9.0)
+
 LIGHTNING_ONLY = config([layer(lightning(), None)], width=40, vocab=97)
 LATENT_ONLY = config([layer(latent(), None)], width=40, vocab=97)
 SHARED_LATENT = config([layer(latent(), None), layer(latent(kv_rank=32, kv_from=0), None)], width=40,
