@@ -18,6 +18,13 @@ Only ``c`` and the rotated part are cached (two planes of a paged cache; one wit
 is folded into the query (``q_lat = W_uk^T q_plain``, a batched product over heads), the kernel
 attends over ``[c | r]`` with values ``c``, and the value up-projection (a second batched product)
 follows: keys and values of the heads are never formed.
+
+Long portions of a design without a rotated part (bfloat16, head sizes up to 128) take the other
+order: the step's requests' cached latent vectors are gathered, ``k = W_uk c`` and ``v = W_uv c``
+are formed for them by two products into a scratch cache of the step, and the grouped-query
+attention kernels (tcgen05 for prompts) run over that.  Heads narrower than the kernels' 64 or 128
+channels are padded with zero rows of the up-projections (and zero columns of ``W_o``), so nothing
+is copied.  The cache still holds ``c`` alone.
 """
 from __future__ import annotations
 
@@ -93,6 +100,28 @@ class LatentAttention(Mixer):
         i = np.arange(self.rot // 2, dtype=np.float64)
         freq = np.power(np.float64(self.base), -2.0 * i / self.rot).astype(np.float32)
         self.freq = torch.from_numpy(freq).to(device)
+        # keys and values formed for long portions: up-projections padded to the kernels' head size
+        self.HDp = 0
+        widest = max(D, Vd)
+        if (self.R == 0 and self.Q and not self.classic and self.uk.dtype == torch.bfloat16
+                and widest <= 128):
+            P = self.HDp = 64 if widest <= 64 else 128
+
+            def rows(w, n):          # [H * n, in] -> [H * P, in], zero rows behind each head's n
+                if n == P:
+                    return w
+                out = torch.zeros((H, P, w.shape[1]), dtype=w.dtype, device=w.device)
+                out[:, :n] = w.view(H, n, w.shape[1])
+                return out.view(H * P, w.shape[1])
+            self.uq_wide = ops.Linear(rows(tensors[self._n("uq")], D))
+            self.uk_wide = rows(tensors[self._n("uk")], D).contiguous()
+            self.uv_wide = rows(tensors[self._n("uv")], Vd).contiguous()
+            wo = tensors[self._n("o")]
+            if Vd != P:
+                wide = torch.zeros((wo.shape[0], H, P), dtype=wo.dtype, device=wo.device)
+                wide[:, :, :Vd] = wo.view(wo.shape[0], H, Vd)
+                wo = wide.view(wo.shape[0], H * P)
+            self.out_wide = ops.Linear(wo, None, out_dtype=torch.float32)
 
     def cache_spec(self):
         if self.R == 0:
@@ -116,6 +145,12 @@ class LatentAttention(Mixer):
             write = cache.write and self.own
             cq = latent.norms(qd, 0, self.Q, self.q_w, self.c_col, C, self.latent_w, self.eps,
                               cache.slot_mapping if write else None, c_pages)
+            if self.HDp and x.dtype == torch.bfloat16 and ctx.max_q_len >= FORMED_MIN_QUERY_ROWS:
+                o = self._over_formed_keys(cq, ctx, cache, c_pages)
+                if o is not None:
+                    if self.gated:
+                        prenorm.head_gate(o, qd[:, self.g_col:self.g_col + H], H, self.HDp)
+                    return self.out_wide(o)
             q_all = self.uq(cq) if self.Q else qd
         q_plain = q_all[:, :H * (D + R)].unflatten(1, (H, D + R))[:, :, :D].transpose(0, 1)
         q_lat = ops.bmm_f32_out(q_plain, self.uk)                 # [H, T, C] fp32
@@ -126,6 +161,43 @@ class LatentAttention(Mixer):
         if self.gated:
             prenorm.head_gate(o, qd[:, self.g_col:self.g_col + H], H, self.Vd)
         return self.out(o)
+
+
+    def _over_formed_keys(self, cq, ctx, cache, c_pages):
+        """Attention of a step with long portions over keys and values formed from the cached
+        latent vectors -> ``[T, H * HDp]``, or ``None`` where the scratch would be too large.
+        Request ``b`` owns the pages ``b W .. (b + 1) W - 1`` of the scratch, ``W`` the pages the
+        longest request of the step holds (under graph capture: the block table's width); what
+        lies behind a request's last token is formed from whatever the table names there and is
+        never seen."""
+        from ..ops import attention_bf16
+        H, P, C = self.H, self.HDp, self.C
+        page, table = cache.page_size, cache.block_table
+        B = ctx.num_seqs
+        if ctx.capturing or not ctx.q_lens_host:
+            W = table.shape[1]
+        else:
+            longest = max(a + n for a, n in zip(ctx.q_starts_host, ctx.q_lens_host))
+            W = min(table.shape[1], -(-longest // page))
+        rows = B * W * page
+        if rows > FORMED_MAX_ROWS or not attention_bf16.supports(P, H, H):
+            return None
+        dev = c_pages.device
+        slots = (table[:B, :W].clamp(0, c_pages.shape[0] - 1).long()[:, :, None] * page
+                 + torch.arange(page, device=dev)).reshape(-1)
+        c = c_pages.view(-1, C).index_select(0, slots)                      # [rows, C]
+        kv = torch.empty((2, B * W, page, H, P), dtype=c.dtype, device=dev)
+        torch.mm(c, self.uk_wide.t(), out=kv[0].view(rows, H * P))
+        torch.mm(c, self.uv_wide.t(), out=kv[1].view(rows, H * P))
+        own = torch.arange(B * W, dtype=torch.int32, device=dev).view(B, W)
+        q = self.uq_wide(cq)
+        return attention_bf16.try_run(q, kv, own, ctx, H, H, P, self.scale, cache.window, page)
+
+
+# Portions of at least this many rows take the formed keys (the tcgen05 prompt kernel's tile),
+# and a step's scratch holds at most this many tokens' keys and values.
+FORMED_MIN_QUERY_ROWS = 64
+FORMED_MAX_ROWS = 1 << 17
 
 
 register_mixer("latent_attention", LatentAttention)

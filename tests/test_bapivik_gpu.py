@@ -194,6 +194,27 @@ def test_long_decoding_past_windows_and_pages_through_graphs(tmp_path_factory, n
     assert runner.graph_launches > 0
 
 
+@pytest.mark.parametrize("name", ["WIDE", "MIXED"])
+def test_equal_prompts_replay_a_graph_of_the_whole_step(tmp_path_factory, name):
+    """Prompts of one length, one a step: from the second on the step is captured and replayed
+    (latent attention over keys formed for the block table's whole width, the tensor-core prompt
+    kernels), then decoded tokens follow; pages and slots are used again."""
+    cfg = getattr(tb, name)
+    d = folder(tmp_path_factory, name, cfg, "bfloat16")
+    reqs = prompts(cfg["vocab"], [300, 300, 300, 300, 300], seed=31)
+    steps = []
+    for rid, toks in reqs.items():
+        steps.append({"step": len(steps), "end": [], "entries": [
+            {"id": rid, "tokens": toks[:288], "want": list(range(288))}]})
+        for i in range(288, 300):
+            steps.append({"step": len(steps), "end": [rid] if i == 299 else [], "entries": [
+                {"id": rid, "tokens": [toks[i]], "want": [0]}]})
+    runner = make_runner(d, "bfloat16", replay.peak_tokens(steps), eager=False)
+    rows = replay.run_in_process(runner, steps)
+    check(rows, expected(d, cfg, reqs), "bfloat16", reqs)
+    assert any(isinstance(k[0], str) for k in runner._graphs), "no portion step was captured"
+
+
 def test_trace_program(tmp_path_factory, tmp_path):
     cfg = tb.OTHER
     d = folder(tmp_path_factory, "OTHER", cfg, "float32")
