@@ -150,6 +150,33 @@ __global__ void silu_f32_kernel(const T* __restrict__ proj, int ld, int rows, in
   out[i] = z * ds_sigmoid(z);
 }
 
+// The same from bfloat16 rows, eight channels a thread (one 16-byte load, two 16-byte stores):
+// width and ld multiples of 8, aligned rows.
+__global__ void silu_f32_vec_kernel(const __nv_bfloat16* __restrict__ proj, int ld, int rows,
+                                    int width, float* __restrict__ out) {
+  const int w8 = width >> 3;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  // No early trigger: the recurrence that follows is a few long-lived blocks, each a chain of
+  // dependent steps.  Let in while this grid still fills the SMs, they land several to an SM on
+  // the first SMs that drain and the chains share issue slots (measured on a 2,048-token prompt:
+  // the recurrence then takes twice as long); after this grid's end they spread one to an SM.
+  pdl_wait();
+  if (i >= (size_t)rows * w8) return;
+  const int r = (int)(i / w8), c = (int)(i - (size_t)r * w8) * 8;
+  const uint4 raw = *reinterpret_cast<const uint4*>(proj + (size_t)r * ld + c);
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  float z[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(p[j]);
+    z[2 * j] = f.x * ds_sigmoid(f.x);
+    z[2 * j + 1] = f.y * ds_sigmoid(f.y);
+  }
+  float4* dst = reinterpret_cast<float4*>(out + (size_t)r * width + c);
+  dst[0] = make_float4(z[0], z[1], z[2], z[3]);
+  dst[1] = make_float4(z[4], z[5], z[6], z[7]);
+}
+
 // ------------------------------------------------------------------------------- the recurrence
 struct DecayDims {
   int H, G, D, Vd;
@@ -499,6 +526,11 @@ GF_EXPORT int gf_silu_f32(const void* proj, int ld, int T, int width, float* out
   if (dtype == GF_F32)
     return launch_kernel(silu_f32_kernel<float>, grid, block, 0, st, (const float*)proj, ld, T,
                          width, out);
+  if (width % 8 == 0 && ld % 8 == 0 && (uintptr_t)proj % 16 == 0 && (uintptr_t)out % 16 == 0) {
+    const dim3 vgrid((unsigned)((total / 8 + 255) / 256));
+    return launch_kernel(silu_f32_vec_kernel, vgrid, block, 0, st, (const bf*)proj, ld, T, width,
+                         out);
+  }
   return launch_kernel(silu_f32_kernel<bf>, grid, block, 0, st, (const bf*)proj, ld, T, width, out);
 }
 

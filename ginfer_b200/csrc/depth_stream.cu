@@ -49,6 +49,7 @@ struct DepthMix {
 // Generic form: the row in shared memory.
 template <typename Y, typename T>
 __global__ void sandwich_kernel(const float* __restrict__ x, const Y* __restrict__ y,
+                                const float* __restrict__ y_bias,
                                 const float* __restrict__ gamma_b, float eps, DepthMix mix,
                                 float* __restrict__ out, const float* __restrict__ gamma_next,
                                 float eps_next, T* __restrict__ normed, int H) {
@@ -60,7 +61,7 @@ __global__ void sandwich_kernel(const float* __restrict__ x, const Y* __restrict
   const size_t base = (size_t)r * H;
   float ss = 0.f;
   for (int j = threadIdx.x; j < H; j += blockDim.x) {
-    const float v = to_f32(y[base + j]);
+    const float v = to_f32(y[base + j]) + (y_bias ? y_bias[j] : 0.f);
     row[j] = v;
     ss += v * v;
   }
@@ -90,6 +91,7 @@ __global__ void sandwich_kernel(const float* __restrict__ x, const Y* __restrict
 // threads, 16-byte aligned rows.
 template <typename Y, typename T, int OPT>
 __global__ void sandwich_vec_kernel(const float* __restrict__ x, const Y* __restrict__ y,
+                                    const float* __restrict__ y_bias,
                                     const float* __restrict__ gamma_b, float eps, DepthMix mix,
                                     float* __restrict__ out, const float* __restrict__ gamma_next,
                                     float eps_next, T* __restrict__ normed, int H) {
@@ -110,6 +112,12 @@ __global__ void sandwich_vec_kernel(const float* __restrict__ x, const Y* __rest
     const int q = threadIdx.x + u * blockDim.x;
     if (q < nq) {
       Quad<Y>::load(y + base + 4 * q, v[u]);
+      if (y_bias) {
+        float b[4];
+        Quad<float>::load(y_bias + 4 * q, b);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[u][i] += b[i];
+      }
 #pragma unroll
       for (int i = 0; i < 4; ++i) ss += v[u][i] * v[u][i];
     }
@@ -191,10 +199,12 @@ GF_EXPORT int gf_embedding_pos(const int* ids, const int* positions, const void*
                        (const bf*)emb, (const bf*)pos_table, out, gamma, eps, (bf*)normed, H);
 }
 
-// x [R, H] fp32, y [R, H] in y_dtype, gamma_b fp32.  hist / mix_w / n_hist / hist_stride / keep: the
+// x [R, H] fp32, y [R, H] in y_dtype (y_bias, nullable fp32 [H], is added to every row of y first: the
+// bias of a product whose library kernel has no epilogue for it), gamma_b fp32.  hist / mix_w / n_hist / hist_stride / keep: the
 // depth average (mix_w null: none).  out (nullable) [R, H] fp32: the stream afterwards.
 // gamma_next / normed (nullable): the next norm in act_dtype.
-GF_EXPORT int gf_sandwich_update(const float* x, const void* y, int y_dtype, const float* gamma_b,
+GF_EXPORT int gf_sandwich_update(const float* x, const void* y, int y_dtype, const float* y_bias,
+                                 const float* gamma_b,
                                  float eps, const float* hist, const float* mix_w, int n_hist,
                                  long long hist_stride, float* keep, float* out,
                                  const float* gamma_next, float eps_next, void* normed, int act_dtype,
@@ -204,7 +214,7 @@ GF_EXPORT int gf_sandwich_update(const float* x, const void* y, int y_dtype, con
   if (act_dtype == GF_F32 && y_dtype != GF_F32) return -2;
   auto st = (cudaStream_t)stream;
   DepthMix mix{hist, mix_w, keep, mix_w ? n_hist : 0, (size_t)hist_stride};
-  const bool al = ((uintptr_t)x | (uintptr_t)y | (uintptr_t)gamma_b | (uintptr_t)out |
+  const bool al = ((uintptr_t)x | (uintptr_t)y | (uintptr_t)y_bias | (uintptr_t)gamma_b | (uintptr_t)out |
                    (uintptr_t)keep | (uintptr_t)hist | (uintptr_t)gamma_next |
                    (uintptr_t)normed) % 16 == 0 && hist_stride % 4 == 0;
   if (H % 4 == 0 && H <= 4 * 4 * 256 && al) {
@@ -212,7 +222,7 @@ GF_EXPORT int gf_sandwich_update(const float* x, const void* y, int y_dtype, con
     const dim3 vgrid(R), vblock(nq <= 128 ? 128 : 256);
 #define GF_VEC(Y, T, OPT)                                                                        \
   return launch_kernel(sandwich_vec_kernel<Y, T, OPT>, vgrid, vblock, 0, st, x, (const Y*)y,      \
-                       gamma_b, eps, mix, out, gamma_next, eps_next, (T*)normed, H)
+                       y_bias, gamma_b, eps, mix, out, gamma_next, eps_next, (T*)normed, H)
 #define GF_OPT(Y, T)                                  \
   {                                                   \
     if (nq <= (int)vblock.x) GF_VEC(Y, T, 1);         \
@@ -229,8 +239,8 @@ GF_EXPORT int gf_sandwich_update(const float* x, const void* y, int y_dtype, con
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 48 * 1024) return -4;
 #define GF_GO(Y, T)                                                                              \
-  return launch_kernel(sandwich_kernel<Y, T>, grid, block, smem, st, x, (const Y*)y, gamma_b, eps, \
-                       mix, out, gamma_next, eps_next, (T*)normed, H)
+  return launch_kernel(sandwich_kernel<Y, T>, grid, block, smem, st, x, (const Y*)y, y_bias,      \
+                       gamma_b, eps, mix, out, gamma_next, eps_next, (T*)normed, H)
   if (act_dtype == GF_F32) GF_GO(float, float);
   if (y_dtype == GF_F32) GF_GO(float, bf);
   GF_GO(bf, bf);

@@ -42,14 +42,17 @@ def embedding_positions(token_ids: torch.Tensor, positions: torch.Tensor, weight
 
 def sandwich_update(x: torch.Tensor, y: torch.Tensor, gamma_b: torch.Tensor, eps: float,
                     act_dtype: torch.dtype, *, history=None, mix_weights=None, n_before: int = 0,
-                    next_weight=None, next_eps: float = 0.0, want_out: bool = True):
-    """The end of a sublayer on the fp32 stream ``x [R, H]``: ``v = x + y * gamma_b / rms(y)``.
+                    next_weight=None, next_eps: float = 0.0, want_out: bool = True, y_bias=None):
+    """The end of a sublayer on the fp32 stream ``x [R, H]``: ``v = x + y * gamma_b / rms(y)``
+    (``y_bias``, fp32 ``[H]``: added to every row of ``y`` first).
     With ``history [states, R, H]`` and ``mix_weights [n_before + 1]`` (fp32), ``v`` is stored as
     state ``n_before`` of the history and the stream becomes ``sum_j mix_weights[j] * state_j``
     over the states ``0 .. n_before``.  With ``next_weight`` (fp32 ``[H]``) the RMS norm of the new
     stream is formed in the same pass.  Returns ``(stream or None, normed in act_dtype or
     None)``."""
-    _cuda(x, y, gamma_b, history, mix_weights, next_weight)
+    _cuda(x, y, gamma_b, history, mix_weights, next_weight, y_bias)
+    assert y_bias is None or (y_bias.dtype == torch.float32 and y_bias.numel() == x.shape[1]
+                              and y_bias.is_contiguous())
     assert x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous()
     assert y.shape == x.shape and y.is_contiguous()
     R, H = x.shape
@@ -68,9 +71,9 @@ def sandwich_update(x: torch.Tensor, y: torch.Tensor, gamma_b: torch.Tensor, eps
         assert next_weight.dtype == torch.float32 and next_weight.numel() == H
         normed = torch.empty((R, H), dtype=act_dtype, device=x.device)
     f = _fn("depth_stream", "gf_sandwich_update",
-            [c_void_p, c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_longlong,
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_longlong,
              c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p])
-    rc = f(_p(x), _p(y), _code(y.dtype), _p(gamma_b), float(eps), _p(hist), _p(mix_weights),
+    rc = f(_p(x), _p(y), _code(y.dtype), _p(y_bias), _p(gamma_b), float(eps), _p(hist), _p(mix_weights),
            int(n_before), stride, _p(keep), _p(out), _p(next_weight), float(next_eps), _p(normed),
            _code(act_dtype), R, H, _stream())
     if rc == -4:

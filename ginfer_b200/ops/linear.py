@@ -70,6 +70,21 @@ class Linear:
         from . import activation_
         return activation_(self._product(x), self.activation)
 
+    def deferring_bias(self, x):
+        """``(y, b)`` with ``self(x) = y + b``: ``b`` is the fp32 bias where adding it would cost a
+        pass of its own (the library's product with fp32 results has no epilogue for it) and the
+        caller can fold it into the kernel that reads ``y`` next; ``None`` where the product has
+        added it."""
+        if (self.activation is None and self.dtype == torch.bfloat16 and self.bias is not None
+                and self.out_dtype == torch.float32 and not hasattr(x, "materialize")
+                and x.dtype == self.dtype):
+            from . import gemm_bf16
+            y = gemm_bf16.try_linear(x, self.weight, self._bias_f32, self.out_dtype)
+            if y is not None:
+                return y, None
+            return torch.mm(x, self.weight.t(), out_dtype=torch.float32), self._bias_f32
+        return self(x), None
+
     def _product(self, x) -> torch.Tensor:
         if hasattr(x, "materialize"):                 # a normalisation not computed yet
             if self.dtype == torch.bfloat16 and x.scaled is not None:

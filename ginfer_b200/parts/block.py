@@ -369,10 +369,11 @@ class SandwichBlock(Block):
         if self.depth_states:
             self.depth_w = tensors[self.depth_name].float().contiguous()
 
-    def _end(self, x, y, out_norm, ctx, nxt, average=False):
-        """One sublayer's end -> ``(stream, norm of the stream for ``nxt`` or None)``."""
+    def _end(self, x, y, out_norm, ctx, nxt, average=False, y_bias=None):
+        """One sublayer's end -> ``(stream, norm of the stream for ``nxt`` or None)``.  ``y_bias``:
+        a bias the sublayer left for this kernel to add to its output."""
         from ..ops import depth
-        kw = {}
+        kw = {"y_bias": y_bias} if y_bias is not None else {}
         if average and self.depth_states:
             hist = ctx.extras.get("depth_history")
             if hist is None or hist.shape[0] < self.depth_states:
@@ -400,8 +401,12 @@ class SandwichBlock(Block):
         a = self.mixer.forward(n, ctx, cache)
         if self.feed_forward is not None:
             x, n2 = self._end(x, a, self.mixer_out_norm, ctx, self.feed_forward_norm)
-            f = self.feed_forward.forward(n2, ctx)
-            x, n_next = self._end(x, f, self.feed_forward_out_norm, ctx, then, average=True)
+            if getattr(self.feed_forward, "can_defer_bias", False):
+                f, fb = self.feed_forward.forward(n2, ctx, defer_bias=True)
+            else:
+                f, fb = self.feed_forward.forward(n2, ctx), None
+            x, n_next = self._end(x, f, self.feed_forward_out_norm, ctx, then, average=True,
+                                  y_bias=fb)
         else:
             x, n_next = self._end(x, a, self.mixer_out_norm, ctx, then, average=True)
         if n_next is not None:

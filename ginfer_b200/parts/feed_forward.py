@@ -110,7 +110,13 @@ class DenseActivationMLP(FeedForward):
         self.up = ops.Linear(tensors[self.up_key], b(self.up_key), activation=self.activation)
         self.down = ops.Linear(tensors[self.down_key], b(self.down_key), out_dtype=torch.float32)
 
-    def forward(self, x, ctx):
+    can_defer_bias = True
+
+    def forward(self, x, ctx, defer_bias: bool = False):
+        """``defer_bias``: returns ``(y, b)`` whose sum is the result, ``b`` the down-projection's
+        bias where the caller's next kernel can add it for nothing (else ``None``)."""
+        if defer_bias:
+            return self.down.deferring_bias(self.up(x))
         return self.down(self.up(x))
 
 

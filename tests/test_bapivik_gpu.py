@@ -418,6 +418,10 @@ def test_sublayer_end_norm_sum_average_and_next_norm(ydt, H):
     v = x.double() + rms(y.double(), wb.double(), 1e-3)
     out, n = depth.sandwich_update(x.cuda(), y.cuda(), wb.cuda(), 1e-3, ydt)
     assert n is None and torch.allclose(out.double().cpu(), v, atol=1e-5)
+    yb = torch.randn(H, generator=g)                  # a bias left for this kernel to add
+    out, n = depth.sandwich_update(x.cuda(), y.cuda(), wb.cuda(), 1e-3, ydt, y_bias=yb.cuda())
+    vb = x.double() + rms(y.double() + yb.double(), wb.double(), 1e-3)
+    assert torch.allclose(out.double().cpu(), vb, atol=1e-5)
     out, n = depth.sandwich_update(x.cuda(), y.cuda(), wb.cuda(), 1e-3, ydt, next_weight=wn.cuda(),
                                    next_eps=1e-5)
     tol = 1e-5 if ydt == torch.float32 else 2e-2
