@@ -48,10 +48,9 @@
 namespace gf {
 
 constexpr int NTHREADS = 192;
-constexpr int EPI_STORE = 0, EPI_SILU = 2, EPI_RESID = 3;
-// (callers may also ask for 1: EPI_STORE whose result, bias included, passes relu(x)^2; the
-// kernel is the same instance and takes the activation as GemmExtra::act)
-constexpr int EPI_RELU2_CODE = 1;
+// EPI_RELU2: EPI_STORE whose result, bias included, passes relu(x)^2 (instances of its own, for
+// the token tiles of decode steps only, so that the plain store keeps its code).
+constexpr int EPI_STORE = 0, EPI_RELU2 = 1, EPI_SILU = 2, EPI_RESID = 3;
 
 struct GemmExtra {
   // consumer of a deferred RMS normalisation: scale[m] = rsqrt(sum_p in_sumsq[p][m] * inv_k + eps)
@@ -66,8 +65,6 @@ struct GemmExtra {
   const void* gamma;         // [N], bf16 or fp32
   int gamma_f32;
   float* out_sumsq;          // [parts][ss_ld]; part = tile of rows (* splits + split)
-  // EPI_STORE
-  int act;                   // 1: the result (with its bias) passes relu(x)^2 before it is stored
 };
 __device__ __forceinline__ float relu2(float x) {
   x = fmaxf(x, 0.f);
@@ -141,14 +138,14 @@ __device__ __forceinline__ void epilogue16(float (&v)[16], OUT* __restrict__ out
 #pragma unroll
     for (int j = 0; j < 16; ++j) v[j] *= scale[j];
   }
-  if (EPI == EPI_STORE) {
+  if (EPI == EPI_STORE || EPI == EPI_RELU2) {
     const float b = (bias && n < N) ? bias[n] : 0.f;
     if (n < N) {
 #pragma unroll
       for (int j = 0; j < 16; ++j)
         if (m_base + j < M)
           store_out<OUT>(out + (size_t)(m_base + j) * ldo + n,
-                         ex.act ? relu2(v[j] + b) : v[j] + b);
+                         EPI == EPI_RELU2 ? relu2(v[j] + b) : v[j] + b);
     }
   } else if (EPI == EPI_RESID) {
     const float b = (bias && n < N) ? bias[n] : 0.f;
@@ -333,7 +330,7 @@ __device__ __forceinline__ void cluster_reduce(uint32_t red, const float* recv, 
                   if (ex.out_scaled) ex.out_scaled[at + j] = __float2bfloat16_rn(g[j]);
                 }
             }
-          } else if (EPI == EPI_STORE && ex.act) {
+          } else if (EPI == EPI_RELU2) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) v[j] = relu2(v[j]);
             if (vec) {
@@ -859,7 +856,7 @@ static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, con
     GF_CASE(32);
     GF_CASE(64);
   }
-  if (EPI != EPI_RESID) {       // the residual epilogue serves the token tiles of decode steps only
+  if (EPI != EPI_RESID && EPI != EPI_RELU2) {   // these serve the token tiles of decode steps only
     switch (bn) {
       GF_CASE(128);
       GF_CASE(256);
@@ -921,10 +918,8 @@ GF_EXPORT int gf_gemm_bf16_tc_ex(const void* x, int ldx, const void* w, const fl
                                  int gamma_f32, float* out_sumsq) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return -6;
-  const int act = epi == EPI_RELU2_CODE ? 1 : 0;
-  if (act) epi = EPI_STORE;
   if (epi == EPI_SILU && ((N & 1) || out_f32)) return -6;
-  if (epi != EPI_STORE && epi != EPI_SILU && epi != EPI_RESID) return -6;
+  if (epi != EPI_STORE && epi != EPI_RELU2 && epi != EPI_SILU && epi != EPI_RESID) return -6;
   const int bn = gf_gemm_bf16_token_tile(M);
   if (split_k < 1) split_k = 1;
   if (epi == EPI_RESID) {
@@ -951,7 +946,6 @@ GF_EXPORT int gf_gemm_bf16_tc_ex(const void* x, int ldx, const void* w, const fl
   ex.gamma = gamma;
   ex.gamma_f32 = gamma_f32;
   ex.out_sumsq = out_sumsq;
-  ex.act = act;
   auto st = (cudaStream_t)stream;
   float* ws = (float*)workspace;
   if (epi == EPI_SILU)
@@ -960,6 +954,13 @@ GF_EXPORT int gf_gemm_bf16_tc_ex(const void* x, int ldx, const void* w, const fl
   if (epi == EPI_RESID)
     return dispatch_bn<EPI_RESID, float>(bn, mw, mx, bias, out, ldo, M, N, K, split_k, ws, err, st,
                                          ex);
+  if (epi == EPI_RELU2) {
+    if (out_f32)
+      return dispatch_bn<EPI_RELU2, float>(bn, mw, mx, bias, out, ldo, M, N, K, split_k, ws, err,
+                                           st, ex);
+    return dispatch_bn<EPI_RELU2, bf16>(bn, mw, mx, bias, out, ldo, M, N, K, split_k, ws, err, st,
+                                        ex);
+  }
   if (out_f32)
     return dispatch_bn<EPI_STORE, float>(bn, mw, mx, bias, out, ldo, M, N, K, split_k, ws, err, st,
                                          ex);
