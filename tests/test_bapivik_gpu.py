@@ -139,8 +139,13 @@ def cuts(reqs):
     mixed, _ = replay.cut_mixed(reqs, seed=3, decode_tail=20)
     singles, _ = replay.cut_mixed(reqs, seed=5, decode_tail=9, singles_first=True,
                                   sizes=(2, 2, 3, 17, 40))
+    # portions long enough for the tensor-core prompt kernels beside single tokens, in both orders
+    long_a, _ = replay.cut_mixed(reqs, seed=9, decode_tail=10, singles_first=True,
+                                 sizes=replay.LONG_SIZES)
+    long_b, _ = replay.cut_mixed(reqs, seed=10, decode_tail=6, sizes=(64, 80, 65))
     return {"whole": replay.cut_whole(reqs), "decode": replay.cut_tail_decode(reqs, tail=40),
-            "portions": replay.cut_portions(reqs), "mixed": mixed, "mixed_singles_first": singles}
+            "portions": replay.cut_portions(reqs), "mixed": mixed, "mixed_singles_first": singles,
+            "mixed_long_singles_first": long_a, "mixed_long": long_b}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
