@@ -390,7 +390,7 @@ def rms(x, w, eps):
 def test_embedding_with_learned_positions(store):
     from ginfer_b200.ops import depth
     g = torch.Generator().manual_seed(0)
-    for H in (40, 320, 1030):
+    for H in (40, 328, 1030):
         E = torch.randn(57, H, generator=g).to(store)
         P = torch.randn(91, H, generator=g).to(store)
         ids = torch.randint(0, 57, (23,), generator=g).int()
@@ -523,7 +523,7 @@ def test_latent_norms_and_the_cache_write():
     from ginfer_b200.ops import latent
     g = torch.Generator().manual_seed(2)
     for dt in (torch.float32, torch.bfloat16):
-        for Q, C in ((24, 32), (33, 20), (96, 128), (0, 64), (768, 512)):
+        for Q, C in ((24, 32), (33, 20), (88, 136), (0, 64), (768, 512)):
             T, slots = 11, 30
             ld = Q + C + 8
             proj = (torch.randn(T, ld, generator=g) * 2).to(dt)
