@@ -171,6 +171,34 @@ __global__ void latent_norms_kernel(const T* __restrict__ proj, int ld, int q_co
   }
 }
 
+// The latent vectors of the step's requests side by side: row (b W + j) page + r of `out` is row r
+// of the page that request b's block table names at j (clamped to the pool: what lies behind a
+// request's last page is copied from somewhere and never read as a key).  `own[b W + j] = b W + j`
+// is the block table under which `out`, seen as B W pages, is a cache of its own.  One block a
+// row; 16 bytes an access where rows allow (`vec`).
+__global__ void latent_gather_kernel(const unsigned char* __restrict__ c_pages,
+                                     const int* __restrict__ table, int table_stride, int W,
+                                     int page, int row_bytes, int num_pages, int vec,
+                                     unsigned char* __restrict__ out, int* __restrict__ own) {
+  const int row = blockIdx.x;
+  const int lp = row / page, r = row - lp * page;         // lp = b W + j
+  const int b = lp / W, j = lp - b * W;
+  pdl_trigger();
+  pdl_wait();
+  int pg = table[(size_t)b * table_stride + j];
+  pg = pg < 0 ? 0 : (pg >= num_pages ? num_pages - 1 : pg);
+  const unsigned char* src = c_pages + ((size_t)pg * page + r) * row_bytes;
+  unsigned char* dst = out + (size_t)row * row_bytes;
+  if (vec) {
+    for (int i = threadIdx.x * 16; i < row_bytes; i += blockDim.x * 16)
+      *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+  } else {
+    for (int i = threadIdx.x * 2; i < row_bytes; i += blockDim.x * 2)
+      *reinterpret_cast<unsigned short*>(dst + i) = *reinterpret_cast<const unsigned short*>(src + i);
+  }
+  if (r == 0 && threadIdx.x == 0) own[lp] = lp;
+}
+
 template <typename T>
 __global__ void latent_attention_kernel(const float* __restrict__ q_lat,   // [H, T, C]
                                         const float* __restrict__ q_rot,   // [T, H, R]
@@ -609,6 +637,22 @@ GF_EXPORT int gf_latent_norms(const void* proj, int ld, int q_col, int Q, const 
   if (pairs) GF_NORMS(bf, true);
   GF_NORMS(bf, false);
 #undef GF_NORMS
+}
+
+// c_pages [num_pages, page, C] (elements of `elem_bytes`: 2 or 4), table [B, table_stride] ->
+// out [B W page, C], own [B W].
+GF_EXPORT int gf_latent_gather(const void* c_pages, const int* table, int table_stride, int B,
+                               int W, int page, int C, int elem_bytes, int num_pages, void* out,
+                               int* own, void* stream) {
+  if (B <= 0 || W <= 0) return 0;
+  if (page <= 0 || C <= 0 || num_pages <= 0 || (elem_bytes != 2 && elem_bytes != 4)) return -3;
+  const long long rows = (long long)B * W * page;
+  if (rows >= (1ll << 31)) return -3;
+  const int row_bytes = C * elem_bytes;
+  const int vec = row_bytes % 16 == 0 && (uintptr_t)c_pages % 16 == 0 && (uintptr_t)out % 16 == 0;
+  return launch_kernel(latent_gather_kernel, dim3((unsigned)rows), dim3(row_bytes >= 1024 ? 64 : 32),
+                       0, (cudaStream_t)stream, (const unsigned char*)c_pages, table, table_stride,
+                       W, page, row_bytes, num_pages, vec, (unsigned char*)out, own);
 }
 
 GF_EXPORT int gf_latent_attention(const float* q_lat, const float* q_rot, const void* c_pages,

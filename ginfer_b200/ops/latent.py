@@ -57,6 +57,29 @@ def norms(proj: torch.Tensor, q_col: int, Q: int, q_w, c_col: int, C: int, c_w, 
     return cq
 
 
+def gather_pages(c_pages: torch.Tensor, block_table: torch.Tensor, B: int, W: int):
+    """The latent vectors that the first ``W`` entries of the ``B`` requests' block tables name,
+    side by side: ``(c [B * W * page, C], own [B, W])``, ``own`` the block table under which ``c``,
+    seen as ``B * W`` pages, is a cache of its own (request ``b`` owns pages ``b W .. b W + W -
+    1``).  Entries behind a request's last page are clamped to the pool and never read as keys."""
+    _cuda(c_pages, block_table)
+    assert c_pages.is_contiguous() and block_table.dtype == torch.int32
+    assert block_table.stride(1) == 1 and B <= block_table.shape[0] and W <= block_table.shape[1]
+    num_pages, page, C = c_pages.shape[0], c_pages.shape[1], c_pages.shape[-1]
+    assert c_pages.numel() == num_pages * page * C
+    c = torch.empty((B * W * page, C), dtype=c_pages.dtype, device=c_pages.device)
+    own = torch.empty((B, W), dtype=torch.int32, device=c_pages.device)
+    f = _fn("latent_attention", "gf_latent_gather",
+            [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+             c_void_p, c_void_p])
+    rc = f(_p(c_pages), _p(block_table), block_table.stride(0), int(B), int(W), page, C,
+           c_pages.element_size(), num_pages, _p(c), _p(own), _stream())
+    if rc == -3:
+        raise ValueError(f"gather of {B} x {W} pages of {page} x {C}")
+    _ok(rc, "latent_gather")
+    return c, own
+
+
 KEY_TILE = 64           # keys a tile of the tensor-core kernel
 MAX_SPLITS = 8
 MIN_TILES_A_SPLIT = 4   # a share shorter than this costs more in the merge than it saves

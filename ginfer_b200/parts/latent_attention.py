@@ -182,14 +182,10 @@ class LatentAttention(Mixer):
         rows = B * W * page
         if rows > FORMED_MAX_ROWS or not attention_bf16.supports(P, H, H):
             return None
-        dev = c_pages.device
-        slots = (table[:B, :W].clamp(0, c_pages.shape[0] - 1).long()[:, :, None] * page
-                 + torch.arange(page, device=dev)).reshape(-1)
-        c = c_pages.view(-1, C).index_select(0, slots)                      # [rows, C]
-        kv = torch.empty((2, B * W, page, H, P), dtype=c.dtype, device=dev)
+        c, own = latent.gather_pages(c_pages, table, B, W)                  # [rows, C], [B, W]
+        kv = torch.empty((2, B * W, page, H, P), dtype=c.dtype, device=c.device)
         torch.mm(c, self.uk_wide.t(), out=kv[0].view(rows, H * P))
         torch.mm(c, self.uv_wide.t(), out=kv[1].view(rows, H * P))
-        own = torch.arange(B * W, dtype=torch.int32, device=dev).view(B, W)
         q = self.uq_wide(cq)
         return attention_bf16.try_run(q, kv, own, ctx, H, H, P, self.scale, cache.window, page)
 

@@ -689,3 +689,21 @@ def test_squared_relu_in_the_products_epilogue(M):
             y32 = ops.Linear(w.float(), bias, activation="relu2")(x.float())
             assert torch.allclose(y32.double(), want, atol=1e-3, rtol=1e-4)
     gemm_bf16.check_errors("cuda:0")
+
+
+def test_latent_vectors_gathered_by_the_block_tables():
+    from ginfer_b200.ops import latent
+    g = torch.Generator().manual_seed(4)
+    for dt in (torch.bfloat16, torch.float32):
+        for C, page in ((32, 4), (20, 8), (512, 16), (6, 2)):
+            pool = 9
+            pages = torch.randn(pool, page, 1, C, generator=g).to(dt)
+            table = torch.randint(0, pool, (5, 7), generator=g).int()
+            table[1, 3] = -1                              # behind a request's last page
+            table[2, 4] = pool + 5
+            for B, W in ((3, 5), (5, 7), (1, 1)):
+                c, own = latent.gather_pages(pages.cuda(), table.cuda(), B, W)
+                assert c.shape == (B * W * page, C) and own.shape == (B, W)
+                assert torch.equal(own.cpu(), torch.arange(B * W, dtype=torch.int32).view(B, W))
+                want = pages[table[:B, :W].clamp(0, pool - 1).long()].reshape(B * W * page, C)
+                assert torch.equal(c.cpu(), want)
